@@ -1,0 +1,199 @@
+/*
+ * lcgemm_b200 -- C ABI of the B200 (sm_100a) rank-7 bilinear GEMM path.
+ *
+ * The reference project (lcgemm) has no native layer: its device code is
+ * generated from Python at run time and its seams call compiled callables with
+ * wrapped tensors (lcgemm/seams/gate_up.py:107-127, lcgemm/seams/down.py:88-102).
+ * The functions below are what a binding for that path would call instead.
+ * Every entry point
+ *   - takes plain device pointers, extents, leading dimensions (in elements)
+ *     and the CUDA stream as `void*` (a cudaStream_t / CUstream);
+ *   - never allocates, frees or synchronises; all launches are asynchronous
+ *     on the given stream;
+ *   - returns LCG_OK (0) or a negative LCG_ERR_* code, with the text of the
+ *     last failure of the calling thread available from lcg_last_error().
+ *
+ * Conventions (the reference's, lcgemm/kernels/sm100.py:3-5): all matrices
+ * are bf16, row-major; activations are (M, K); weights are (N, K) "K-major",
+ * the layout torch.nn.functional.linear stores; accumulation is fp32.
+ *
+ * Plane geometry.  A one-level 2x2x2 scheme splits M, K, N in two blocks.
+ *   M2  = ceil(M / 2)                       rows of one A block
+ *   N2  = round_up(ceil(N / 2), 8)          rows of one B block (and the column
+ *                                           offset of C block j is j * N2)
+ *   K2  = ceil(K / 2),  K2p = round_up(K2, 64)
+ * A planes are a (rank * M2, K2p) matrix, plane r at row r * M2;
+ * B planes are a (rank * N2, K2p) matrix, plane r at row r * N2.  Elements that
+ * fall outside the source matrix, and columns K2..K2p, are zero.  For the
+ * shapes the reference supports (everything divisible) these are exactly the
+ * reference's (R * M/p, K/q) and (R * N/s, K/q) planes (lcgemm/planes.py:54-71,
+ * lcgemm/seams/gate_up.py:82-93).  lcg_plane_geometry() returns the numbers.
+ *
+ * Device status word.  The tcgen05 kernels bound every wait on an mbarrier;
+ * a wait that runs out writes a nonzero code into `status` (one int32 in
+ * device memory, zeroed by the caller before the first launch) and lets the
+ * kernel run to its end without blocking again.  `status` may be NULL.
+ */
+#ifndef LCGEMM_B200_H
+#define LCGEMM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LCG_OK                      0
+#define LCG_ERR_BAD_ARG           (-1)
+#define LCG_ERR_UNSUPPORTED_SHAPE (-2)
+#define LCG_ERR_MISALIGNED        (-3)
+#define LCG_ERR_SCHEME            (-4)
+#define LCG_ERR_CUDA              (-5)
+#define LCG_ERR_DEVICE_TIMEOUT    (-6)
+
+/* Work decomposition of the rank-7 GEMM. */
+#define LCG_SCHEDULE_ALL_RANKS   0  /* one CTA group walks all products of a tile;
+                                       first write to a C block is a store, later
+                                       ones reduce-adds (lcgemm/kernels/sm100.py:10-16,
+                                       lcgemm/kernels/down.py:490-505) */
+#define LCG_SCHEDULE_RANK_SPLIT  1  /* one (product, tile) unit per step, every
+                                       contribution is a reduce-add into a C that
+                                       arrives zeroed (lcgemm/kernels/down_rank_split.py:106-113,209-216) */
+
+/* MMA pairing: 1 = one CTA per 128x256 tile, 2 = a 2-CTA pair per 256x256 tile
+ * (the reference's tcgen05 CtaGroup.TWO, lcgemm/kernels/sm100.py:186-191). */
+#define LCG_CTA_GROUP_DEFAULT 0
+
+typedef struct lcg_scheme lcg_scheme_t;
+
+/* ---- library ----------------------------------------------------------- */
+
+int lcg_version(void);
+
+/* Text of the calling thread's last failure ("" if none). Never NULL. */
+const char* lcg_last_error(void);
+
+/* ---- scheme (replaces lcgemm/scheme.py:121-486 on the native side) ------ */
+
+/* Build a scheme handle from the coefficient tables of a 2x2x2 decomposition:
+ * a, b, c are rank x 4 row-major over (i,k), (k,j), (i,j); `clear` is the
+ * per-step accumulator-chain flag of a postsum plan or NULL for the plain
+ * scatter epilogue (lcgemm/scheme.py:136-139,189-201).  The exact integer
+ * tensor identity (lcgemm/scheme.py:324-361) and the chain plan
+ * (lcgemm/scheme.py:363-408) are validated here as well; a scheme that fails
+ * returns LCG_ERR_SCHEME. */
+int lcg_scheme_create(const int8_t* a, const int8_t* b, const int8_t* c,
+                      int rank, const int8_t* clear, lcg_scheme_t** out);
+void lcg_scheme_destroy(lcg_scheme_t* scheme);
+
+/* The derived epilogue plan, for cross-checking against the host-side Scheme
+ * (lcgemm/scheme.py:250-264 `epi_groups`).  Writes, per step, up to 4 records
+ * (bi, bj, coeff, is_first) into out[step*16 + 4*n ..]; counts[step] receives
+ * the number of records. */
+int lcg_scheme_plan(const lcg_scheme_t* scheme, int8_t* out, int32_t* counts);
+
+/* ---- geometry ---------------------------------------------------------- */
+
+/* rows2 = ceil(rows/2) rounded up to `row_align` (1 for A, 8 for B);
+ * k2 = ceil(cols/2); k2p = round_up(k2, 64). */
+int lcg_plane_geometry(int64_t rows, int64_t cols, int row_align,
+                       int64_t* rows2, int64_t* k2, int64_t* k2p);
+
+/* ---- operand planes ----------------------------------------------------- */
+
+/* B planes of a static weight, fp32 sum and one rounding
+ * (lcgemm/planes.py:54-71 `prepare_b`).  w is (N, K) with leading dimension
+ * ldw; out is (rank * N2, ld_out) with ld_out >= K2p. */
+int lcg_prepare_b(const lcg_scheme_t* scheme, const void* w, int64_t N, int64_t K,
+                  int64_t ldw, void* out, int64_t ld_out, void* stream);
+
+/* A planes of a plain activation matrix (no counterpart is shipped by the
+ * reference, which removed its standalone A transform, lcgemm/planes.py:16-17;
+ * semantics are those of lcgemm/chain_gauge.py:91-98 without SwiGLU or gauge).
+ * a is (M, K) with leading dimension lda; out is (rank * M2, ld_out). */
+int lcg_a_planes(const lcg_scheme_t* scheme, const void* a, int64_t M, int64_t K,
+                 int64_t lda, void* out, int64_t ld_out, void* stream);
+
+/* Fused residual add + RMSNorm + A planes
+ * (lcgemm/kernels/fused_norm.py:140-198 `fused_norm_residual_kernel`):
+ *   h = bf16(float(delta) + float(residual))      -> residual_out (may alias residual)
+ *   y = float(h) * rsqrt(mean(h^2) + eps) * (float(norm_weight) + 1)
+ *   out plane r = bf16(signed sum of the four blocks of y)
+ * delta, residual, residual_out are contiguous (M, K); needs M even, K % 16 == 0. */
+int lcg_norm_planes(const lcg_scheme_t* scheme, const void* delta, const void* residual,
+                    const void* norm_weight, int64_t M, int64_t K, float eps,
+                    void* residual_out, void* out, int64_t ld_out, void* stream);
+
+/* SwiGLU + the consumer's A planes in the interleaved-K gauge, as a kernel of
+ * its own (lcgemm/chain_gauge.py:82-99 `chain_a_planes`; on the device the
+ * reference fuses this into its GEMM, lcgemm/kernels/sm100.py:820-888).
+ * z is (M, 2*I) = [gate | up] with leading dimension ldz; out is
+ * (rank * M/2, I/2).  Needs M even and I % 128 == 0. */
+int lcg_swiglu_planes(const lcg_scheme_t* plane_scheme, const void* z, int64_t M,
+                      int64_t I, int64_t ldz, void* out, int64_t ld_out, void* stream);
+
+/* ---- GEMMs --------------------------------------------------------------- */
+
+/* Dense C = A @ B^T on tcgen05 (the baseline arm: what the stock model's
+ * cuBLAS GEMM computes, lcgemm/integrate/qwen_patch.py:53-57).  A (M, K),
+ * B (N, K), C (M, N); lda, ldb, ldc multiples of 8; K multiple of 8. */
+int lcg_gemm_dense(const void* a, int64_t lda, const void* b, int64_t ldb,
+                   void* c, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                   int cta_group, int32_t* status, void* stream);
+
+/* Rank-7 C = A @ B^T from prepared planes
+ * (lcgemm/kernels/sm100.py:447-752 mainloop + scatter, lcgemm/kernels/down.py,
+ * lcgemm/kernels/down_rank_split.py).  With LCG_SCHEDULE_RANK_SPLIT the caller
+ * passes C zeroed.  ldc multiple of 8. */
+int lcg_gemm_r7(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,
+                const void* b_planes, int64_t ld_b, void* c, int64_t ldc,
+                int64_t M, int64_t N, int64_t K, int schedule, int cta_group,
+                int32_t* status, void* stream);
+
+/* The chained gate_up GEMM (lcgemm/kernels/sm100.py `LcGemmSm100.call_planes`):
+ * Z = rank-7 product into z (M, N = 2*I), then, in the same kernel, one tile
+ * behind the mainloop, S = silu(Z[:, :I]) * Z[:, I:] and the consumer's A planes
+ * L_r(S) in the interleaved gauge into down_planes (plane_rank * M/2, I/2);
+ * optionally zeroes `preclear` (preclear_bytes, multiple of 16) for a
+ * rank-split consumer (lcgemm/kernels/sm100.py:779-815).
+ * Needs M % 2 == 0, I % 256 == 0, K % 128 == 0. */
+int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_scheme,
+                      const void* a_planes, int64_t ld_a, const void* b_planes, int64_t ld_b,
+                      void* z, int64_t ldz, int64_t M, int64_t N, int64_t K,
+                      void* down_planes, int64_t ld_planes,
+                      void* preclear, int64_t preclear_bytes, int cta_group,
+                      int32_t* status, void* stream);
+
+/* ---- dense-arm seams (the stock layer the rank-7 path is compared with) -- */
+
+/* h = bf16(delta + residual) -> residual_out; x = bf16(rmsnorm(h) * (w + 1))
+ * (lcgemm/integrate/qwen_patch.py:49-52). Contiguous (M, K), K % 8 == 0. */
+int lcg_add_rmsnorm(const void* delta, const void* residual, const void* norm_weight,
+                    int64_t M, int64_t K, float eps, void* residual_out, void* x,
+                    void* stream);
+
+/* s = bf16(silu(float(gate))) * up  (lcgemm/integrate/qwen_patch.py:54-56).
+ * z is (M, 2*I) with ldz; s is (M, I) with lds. I % 8 == 0. */
+int lcg_swiglu(const void* z, int64_t M, int64_t I, int64_t ldz, void* s, int64_t lds,
+               void* stream);
+
+/* out = bf16(float(a) + float(b)), n elements (the residual add that closes
+ * the layer in config form `x + mlp(x)`). n % 8 == 0. */
+int lcg_add(const void* a, const void* b, void* out, int64_t n, void* stream);
+
+/* ---- introspection ------------------------------------------------------- */
+
+/* Kernel launches issued by this library in this process (for the bench's
+ * `gpu_launches`). */
+int64_t lcg_launch_count(void);
+
+/* One line describing the schedule the GEMM entry points would pick for a
+ * shape (tile, stages, units, CTA groups); the counterpart of the reference's
+ * Plan.describe() (lcgemm/kernels/sm100.py:358-374). Returns bytes written. */
+int lcg_describe_gemm(int64_t M, int64_t N, int64_t K, int rank7, int schedule,
+                      int cta_group, char* buf, int buflen);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LCGEMM_B200_H */

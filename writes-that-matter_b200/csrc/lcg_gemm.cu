@@ -1,0 +1,761 @@
+// The tcgen05 GEMM of the path: one persistent, warp-specialised kernel that
+// serves the dense baseline, the rank-7 product walk (all products per tile, or
+// one product per work unit) and the chained gate_up form whose extra warps turn
+// finished Z tiles into the consumer's A planes.
+//
+// Per CTA:  warp 0      TMA producer (one lane)
+//           warp 1      TMEM allocation + tcgen05.mma issue (one lane, pair leader only)
+//           warps 2-5   epilogue: TMEM -> registers -> bf16 -> swizzled smem -> TMA store / reduce-add
+//           warps 6-13  (chain only) SwiGLU + A planes of the tile finished before
+//
+// Data flow per accumulator step t of a work unit:
+//   A plane tile (128 x 64 bf16 per CTA) and B plane tile (256 / group x 64) arrive by TMA
+//   with the 128-byte swizzle, tcgen05.mma accumulates 128 x 256 fp32 per CTA in TMEM stage
+//   t % 2 (a step that does not clear adds to the sum left by step t - 2: the chain
+//   trick of lcgemm/scheme.py:18-40), the epilogue publishes the stage to the C blocks the
+//   plan names (lcgemm/kernels/sm100.py:690-727).
+//
+// Every wait is bounded (lcg_ptx.cuh: mbar_wait); a wait that runs out flags the CTA and
+// the status word and the kernel finishes without blocking again.
+#include <cuda_bf16.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "lcg_common.h"
+#include "lcg_ptx.cuh"
+
+namespace lcg {
+
+constexpr int kBM = 128;        // accumulator rows per CTA = TMEM lanes
+constexpr int kBN = 256;        // accumulator columns per stage
+constexpr int kBK = 64;         // K per pipeline stage (one 128-byte swizzle row)
+constexpr int kUmmaK = 16;      // K per tcgen05.mma, bf16
+constexpr int kEpiCols = 64;    // columns per staged epilogue sub-tile
+constexpr int kEpiBytes = kBM * kEpiCols * 2;
+constexpr int kEpiBufs = 2;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kEpiWarp0 = 2;
+constexpr int kPlaneWarp0 = 6;
+constexpr int kPlaneThreads = 256;
+constexpr int kThreadsPlain = 192;
+constexpr int kThreadsChain = 192 + kPlaneThreads;
+
+// Codes left in the status word by a wait that ran out.
+constexpr int kCodeProducer = 101, kCodeMmaAcc = 102, kCodeMmaFull = 103, kCodeEpilogue = 104,
+              kCodePlane = 105;
+
+template <int kCtaGroup>
+struct Tile {
+  static constexpr int kBRows = kBN / kCtaGroup;        // B rows each CTA loads
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = kBRows * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = kCtaGroup == 1 ? 4 : 6;
+  static constexpr int kTileM = kBM * kCtaGroup;        // rows per work-unit tile
+  static constexpr int kSmemData = kStages * kStageBytes + kEpiBufs * kEpiBytes;
+  static constexpr int kSmemBytes = kSmemData + 256 /*barriers*/ + 1024 /*alignment slack*/;
+};
+
+struct CMaps {
+  CUtensorMap m[4];
+};
+
+struct ChainParams {
+  const __nv_bfloat16* z;     // the GEMM's own output, re-read L2-hot
+  int64_t ldz;
+  __nv_bfloat16* planes;      // (plane_rank * m2, inter / 2)
+  int64_t ld_planes;
+  int32_t m2;                 // rows per block row
+  int32_t inter;              // I: S columns; gate block = z[:, :I], up block = z[:, I:]
+  int32_t plane_rank;
+  int32_t iters_max;          // most tiles any CTA group walks
+  TermTable plane_terms;
+  uint4* preclear;            // consumer output to zero, or null
+  int64_t preclear_vecs;
+};
+
+struct GemmParams {
+  StepDesc steps[kMaxRank];
+  int32_t steps_per_unit;     // 7 (all products per tile) or 1 (dense, rank split)
+  int32_t rank_split;         // unit = product * tiles + tile
+  int32_t tiles_m, tiles_n, group_m;
+  int32_t num_units;
+  int32_t k_blocks;
+  int32_t a_plane_rows, b_plane_rows;
+  int32_t* status;
+  ChainParams chain;
+};
+
+// Work unit -> (first step, tile row, tile column).  Tiles are walked in bands of
+// group_m tile rows, tile row fastest inside a band, so the tiles in flight at any
+// time span a near-square patch and share operand panels in L2
+// (lcgemm/kernels/sm100.py:78-96,754-772).
+struct UnitCoord {
+  int step0, tm, tn;
+};
+__device__ __forceinline__ UnitCoord decode_unit(const GemmParams& p, int u) {
+  const int tiles = p.tiles_m * p.tiles_n;
+  UnitCoord c;
+  int t = u;
+  c.step0 = 0;
+  if (p.rank_split) {
+    c.step0 = u / tiles;
+    t = u - c.step0 * tiles;
+  }
+  const int band_sz = p.group_m * p.tiles_n;
+  const int band = t / band_sz;
+  const int rem = t - band * band_sz;
+  const int gm = min(p.group_m, p.tiles_m - band * p.group_m);
+  c.tm = band * p.group_m + rem % gm;
+  c.tn = rem / gm;
+  return c;
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
+                                             uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& q, float (&f)[8]) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    f[2 * t] = __uint_as_float(w[t] << 16);
+    f[2 * t + 1] = __uint_as_float(w[t] & 0xffff0000u);
+  }
+}
+
+__device__ __forceinline__ float silu_dev(float g) { return g / (1.0f + __expf(-g)); }
+
+template <int kCtaGroup, bool kChain>
+__global__ void __launch_bounds__(kChain ? kThreadsChain : kThreadsPlain, 1)
+k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+       const __grid_constant__ CMaps tma_c, const __grid_constant__ GemmParams p) {
+  using T = Tile<kCtaGroup>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;          // swizzle atoms need 1024-byte alignment
+  uint8_t* smem_gen = smem_raw + (base - raw);
+
+  const uint32_t epi_base = base + T::kStages * T::kStageBytes;
+  const uint32_t bar_base = epi_base + kEpiBufs * kEpiBytes;
+  auto a_smem = [&](uint32_t s) { return base + s * T::kStageBytes; };
+  auto b_smem = [&](uint32_t s) { return base + s * T::kStageBytes + T::kABytes; };
+  auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (T::kStages + s); };
+  auto acc_full_bar = [&](uint32_t s) { return bar_base + 8u * (2 * T::kStages + s); };
+  auto acc_empty_bar = [&](uint32_t s) { return bar_base + 8u * (2 * T::kStages + 2 + s); };
+  const uint32_t misc = bar_base + 8u * (2 * T::kStages + 4);
+  volatile uint32_t* misc_gen =
+      reinterpret_cast<volatile uint32_t*>(smem_gen + (misc - base));
+  // misc_gen[0] = TMEM base, [1] = abort flag, [2] = finished-tile counter
+  const uint32_t z_done_addr = misc + 8;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = kCtaGroup == 2 ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int group_id = blockIdx.x / kCtaGroup;
+  const int num_groups = gridDim.x / kCtaGroup;
+  const WaitCtl ctl{&misc_gen[1], p.status};
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < T::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (uint32_t s = 0; s < 2; ++s) {
+      mbar_init(acc_full_bar(s), 1);
+      mbar_init(acc_empty_bar(s), 4 * kCtaGroup);   // one arrival per epilogue warp of the group
+    }
+    misc_gen[1] = 0u;
+    misc_gen[2] = 0u;
+    fence_mbar_init();
+    prefetch_tensormap(&tma_a);
+    prefetch_tensormap(&tma_b);
+    prefetch_tensormap(&tma_c.m[0]);
+  }
+  if (warp == 1) {
+    tmem_alloc<kCtaGroup>(misc, kTmemCols);
+    tmem_relinquish<kCtaGroup>();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if constexpr (kCtaGroup == 2) {   // the peer's barriers must exist before anyone signals them
+    cluster_arrive();
+    cluster_wait();
+  }
+  tcgen05_fence_after();
+  const uint32_t tmem_base = misc_gen[0];
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int u = group_id; u < p.num_units; u += num_groups) {
+        const UnitCoord uc = decode_unit(p, u);
+        for (int s = uc.step0; s < uc.step0 + p.steps_per_unit; ++s) {
+          const int a_row = p.steps[s].a_plane * p.a_plane_rows + uc.tm * T::kTileM +
+                            static_cast<int>(cta_rank) * kBM;
+          const int b_row = p.steps[s].b_plane * p.b_plane_rows + uc.tn * kBN +
+                            static_cast<int>(cta_rank) * T::kBRows;
+          for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+            const uint32_t stage = it % T::kStages;
+            const uint32_t phase = (it / T::kStages) & 1u;
+            mbar_wait(empty_bar(stage), phase ^ 1u, ctl, kCodeProducer);
+            if constexpr (kCtaGroup == 1) {
+              mbar_arrive_expect_tx(full_bar(stage), T::kStageBytes);
+              tma_load_2d(a_smem(stage), &tma_a, full_bar(stage), kb * kBK, a_row);
+              tma_load_2d(b_smem(stage), &tma_b, full_bar(stage), kb * kBK, b_row);
+            } else {
+              // Both CTAs of the pair post their bytes on the leader's barrier.
+              if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * T::kStageBytes);
+              const uint32_t bar = mapa_shared(full_bar(stage), 0);
+              tma_load_2d_pair(a_smem(stage), &tma_a, bar, kb * kBK, a_row);
+              tma_load_2d_pair(b_smem(stage), &tma_b, bar, kb * kBK, b_row);
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_bf16(kBM * kCtaGroup, kBN);
+      uint32_t it = 0, acc_it = 0;
+      for (int u = group_id; u < p.num_units; u += num_groups) {
+        const UnitCoord uc = decode_unit(p, u);
+        for (int s = uc.step0; s < uc.step0 + p.steps_per_unit; ++s, ++acc_it) {
+          const uint32_t as = acc_it & 1u;
+          const uint32_t aphase = (acc_it >> 1) & 1u;
+          mbar_wait(acc_empty_bar(as), aphase ^ 1u, ctl, kCodeMmaAcc);
+          tcgen05_fence_after();
+          const uint32_t d_tmem = tmem_base + as * kBN;
+          const uint32_t keep = p.steps[s].clear ? 0u : 1u;
+          for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+            const uint32_t stage = it % T::kStages;
+            const uint32_t phase = (it / T::kStages) & 1u;
+            mbar_wait(full_bar(stage), phase, ctl, kCodeMmaFull);
+            tcgen05_fence_after();
+            const uint64_t adesc = make_kmajor_sw128_desc(a_smem(stage));
+            const uint64_t bdesc = make_kmajor_sw128_desc(b_smem(stage));
+#pragma unroll
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              // +32 bytes per K=16 slice inside the 128-byte swizzle row
+              umma_bf16<kCtaGroup>(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc,
+                                   (kb | k) != 0 ? 1u : keep);
+            }
+            umma_commit<kCtaGroup>(empty_bar(stage));   // frees the stage in every CTA of the group
+          }
+          umma_commit<kCtaGroup>(acc_full_bar(as));
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp < kPlaneWarp0) {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;                 // TMEM lanes this warp may touch
+    const int row = quarter * 32 + lane;          // row inside the CTA's 128-row tile
+    const bool issuer = warp == kEpiWarp0 && lane == 0;
+    const uint32_t acc_empty_remote =
+        kCtaGroup == 2 ? mapa_shared(acc_empty_bar(0), 0) : acc_empty_bar(0);
+    uint32_t acc_it = 0, epi_it = 0, tiles_done = 0;
+    for (int u = group_id; u < p.num_units; u += num_groups) {
+      const UnitCoord uc = decode_unit(p, u);
+      const int row0 = uc.tm * T::kTileM + static_cast<int>(cta_rank) * kBM;
+      const int col0 = uc.tn * kBN;
+      for (int s = uc.step0; s < uc.step0 + p.steps_per_unit; ++s, ++acc_it) {
+        const uint32_t as = acc_it & 1u;
+        const uint32_t aphase = (acc_it >> 1) & 1u;
+        mbar_wait(acc_full_bar(as), aphase, ctl, kCodeEpilogue);
+        tcgen05_fence_after();
+        const StepDesc& sd = p.steps[s];
+        for (int g = 0; g < sd.ngroups; ++g) {
+          const float coeff = static_cast<float>(sd.group[g].coeff);
+#pragma unroll 1
+          for (int sub = 0; sub < kBN / kEpiCols; ++sub, ++epi_it) {
+            uint32_t r0[32], r1[32];
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   as * kBN + sub * kEpiCols;
+            tmem_ld_32x32(taddr, r0);
+            tmem_ld_32x32(taddr + 32, r1);
+            tmem_ld_wait();
+            uint32_t pk[32];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              pk[j] = pack_bf16x2(coeff * __uint_as_float(r0[2 * j]),
+                                  coeff * __uint_as_float(r0[2 * j + 1]));
+              pk[16 + j] = pack_bf16x2(coeff * __uint_as_float(r1[2 * j]),
+                                       coeff * __uint_as_float(r1[2 * j + 1]));
+            }
+            const uint32_t buf = epi_base + (epi_it & 1u) * kEpiBytes;
+            // The bulk copy issued two sub-tiles ago read this buffer; it must be done.
+            if (issuer) bulk_wait_group_read<1>();
+            __syncwarp();
+            named_bar_sync(1, 128);
+            const uint32_t row_addr = buf + row * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              st_shared_v4(row_addr + (((c ^ (row & 7)) << 4)), pk[4 * c], pk[4 * c + 1],
+                           pk[4 * c + 2], pk[4 * c + 3]);
+            fence_proxy_async_shared();
+            named_bar_sync(1, 128);
+            if (issuer) {
+              for (int d = 0; d < sd.group[g].ndest; ++d) {
+                const EpiDest dst = sd.group[g].dest[d];
+                const CUtensorMap* cm = &tma_c.m[dst.bi * 2 + dst.bj];
+                if (dst.first)
+                  tma_store_2d(cm, buf, col0 + sub * kEpiCols, row0);
+                else
+                  tma_reduce_add_2d(cm, buf, col0 + sub * kEpiCols, row0);
+              }
+              bulk_commit_group();
+            }
+            __syncwarp();
+          }
+        }
+        // This warp's reads of the stage are complete: hand it back to the MMA issuer.
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (kCtaGroup == 1)
+            mbar_arrive(acc_empty_bar(as));
+          else
+            mbar_arrive_cluster(acc_empty_remote + 8u * as);
+        }
+      }
+      if constexpr (kChain) {
+        // The tile's C blocks are final once every bulk copy has landed; publish
+        // that to the plane warps (single writer per tile, so ordering is CTA-local).
+        if (issuer) {
+          bulk_wait_group<0>();
+          fence_proxy_async_all();
+          st_release_shared(z_done_addr, ++tiles_done);
+        }
+        __syncwarp();
+      }
+    }
+    if (issuer) bulk_wait_group<0>();
+    __syncwarp();
+  } else if constexpr (kChain) {
+    // ------------------------------------------------------------- plane warps
+    // 256 threads; 16 slots across (chunk pair, 8-column vector), 16 rows per step.
+    const ChainParams& ch = p.chain;
+    const int ptid = threadIdx.x - kPlaneWarp0 * 32;
+    const int slot = ptid & 15;
+    const int pair = slot >> 3;
+    const int vc = slot & 7;
+    const int rsub = ptid >> 4;
+    uint32_t tile_no = 0;
+    const int64_t clear_stride =
+        static_cast<int64_t>(gridDim.x) * kPlaneThreads * ch.iters_max;
+    auto clear_share = [&](int t) {
+      if (ch.preclear == nullptr) return;
+      const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+      for (int64_t i = (static_cast<int64_t>(t) * gridDim.x + blockIdx.x) * kPlaneThreads + ptid;
+           i < ch.preclear_vecs; i += clear_stride)
+        ch.preclear[i] = zero;
+    };
+    for (int u = group_id; u < p.num_units; u += num_groups) {
+      const UnitCoord uc = decode_unit(p, u);
+      clear_share(static_cast<int>(tile_no));
+      ++tile_no;
+      counter_wait(z_done_addr, tile_no, ctl, kCodePlane);
+      fence_proxy_async_all();
+      const int row_base = uc.tm * T::kTileM + static_cast<int>(cta_rank) * kBM;
+      const int scol = uc.tn * kBN + pair * 128 + vc * 8;     // S column of chunk h = 0
+      const int pcol = uc.tn * (kBN / 2) + pair * 64 + vc * 8;
+      if (scol + 64 < ch.inter) {
+#pragma unroll 1
+        for (int step = 0; step < kBM / 16; ++step) {
+          const int rho = row_base + rsub + step * 16;
+          if (rho >= ch.m2) break;
+          uint4 q[2][2][2];
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+              for (int hh = 0; hh < 2; ++hh)
+                q[i][j][hh] = __ldcg(reinterpret_cast<const uint4*>(
+                    ch.z + (static_cast<int64_t>(i) * ch.m2 + rho) * ch.ldz +
+                    static_cast<int64_t>(j) * ch.inter + scol + hh * 64));
+          float sv[4][8];
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              float g[8], uu[8];
+              unpack_bf16x8(q[i][0][hh], g);
+              unpack_bf16x8(q[i][1][hh], uu);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) sv[i * 2 + hh][e] = silu_dev(g[e]) * uu[e];
+            }
+          for (int r = 0; r < ch.plane_rank; ++r) {
+            float o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = 0.f;
+            bool started = false;
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              const int cf = ch.plane_terms.coef[r][x];
+              if (cf == 0) continue;
+              const float w = static_cast<float>(cf);
+              if (!started) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = w * sv[x][e];
+                started = true;
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = fmaf(w, sv[x][e], o[e]);
+              }
+            }
+            uint4 outv;
+            outv.x = pack_bf16x2(o[0], o[1]);
+            outv.y = pack_bf16x2(o[2], o[3]);
+            outv.z = pack_bf16x2(o[4], o[5]);
+            outv.w = pack_bf16x2(o[6], o[7]);
+            *reinterpret_cast<uint4*>(ch.planes +
+                                      (static_cast<int64_t>(r) * ch.m2 + rho) * ch.ld_planes +
+                                      pcol) = outv;
+          }
+        }
+      }
+    }
+    for (int t = static_cast<int>(tile_no); t < ch.iters_max; ++t) clear_share(t);
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (misc_gen[1] != 0u && warp == 0) {
+    // A wait ran out somewhere: loads may still be in flight towards this CTA's
+    // shared memory.  Give them time to land before the CTA goes away.
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if constexpr (kCtaGroup == 2) {   // neither CTA may leave while its peer can still signal it
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc<kCtaGroup>(tmem_base, kTmemCols);
+  }
+}
+
+// ============================================================== host side
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(ptr);
+  });
+  return fn;
+}
+
+// bf16 row-major (outer x inner) matrix, 128-byte swizzled boxes of box_outer x 64.
+int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld,
+             int box_outer, const char* what) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return fail(LCG_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
+    return fail(LCG_ERR_MISALIGNED, "%s: base address must be 16-byte aligned", what);
+  if (ld % 8 != 0)
+    return fail(LCG_ERR_MISALIGNED, "%s: leading dimension %lld must be a multiple of 8 elements", what,
+                (long long)ld);
+  if (inner < 1 || outer < 1) return fail(LCG_ERR_UNSUPPORTED_SHAPE, "%s: empty extent", what);
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_outer)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r =
+      fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(LCG_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with CUresult %d", what, (int)r);
+  return LCG_OK;
+}
+
+int sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2)
+      sms = 148;
+  }
+  return sms;
+}
+
+// Tile rows kept open at once: the divisor-free version of "minimise a + groups / a".
+int pick_group_m(int tiles_m, int groups) {
+  int best = 1;
+  double best_cost = 1e30;
+  for (int a = 1; a <= tiles_m; ++a) {
+    if (tiles_m % a != 0) continue;
+    const double cost = a + static_cast<double>(groups) / a;
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = a;
+    }
+  }
+  return best;
+}
+
+template <int kCtaGroup, bool kChain>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CMaps& mc, GemmParams& p,
+           cudaStream_t stream) {
+  using T = Tile<kCtaGroup>;
+  auto kern = k_gemm<kCtaGroup, kChain>;
+  static bool configured[64] = {};   // per device: the attribute belongs to the device's context
+  int dev = 0;
+  LCG_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    LCG_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const int max_groups = sm_count() / kCtaGroup;
+  const int groups = p.num_units < max_groups ? p.num_units : max_groups;
+  if (kChain) p.chain.iters_max = (p.num_units + groups - 1) / groups;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(groups * kCtaGroup));
+  cfg.blockDim = dim3(kChain ? kThreadsChain : kThreadsPlain);
+  cfg.dynamicSmemBytes = T::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCtaGroup;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  LCG_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, p));
+  count_launch();
+  return LCG_OK;
+}
+
+int resolve_group(int cta_group) {
+  if (cta_group == LCG_CTA_GROUP_DEFAULT) return 2;
+  return cta_group;
+}
+
+struct R7Geometry {
+  int64_t m2, n2, k2p;
+};
+
+int r7_geometry(int64_t M, int64_t N, int64_t K, R7Geometry* g) {
+  if (M < 2 || N < 2 || K < 2)
+    return fail(LCG_ERR_UNSUPPORTED_SHAPE, "rank-7 GEMM needs M, N, K >= 2");
+  int64_t k2;
+  lcg_plane_geometry(M, K, 1, &g->m2, &k2, &g->k2p);
+  lcg_plane_geometry(N, K, 8, &g->n2, nullptr, nullptr);
+  if (N - g->n2 < 1)
+    return fail(LCG_ERR_UNSUPPORTED_SHAPE, "N=%lld leaves the second column block empty", (long long)N);
+  if (7 * g->m2 > 0x7fffffffLL || 7 * g->n2 > 0x7fffffffLL)
+    return fail(LCG_ERR_UNSUPPORTED_SHAPE, "operand too tall");
+  return LCG_OK;
+}
+
+int fill_r7(const lcg_scheme* scheme, const void* a_planes, int64_t ld_a, const void* b_planes,
+            int64_t ld_b, void* c, int64_t ldc, int64_t M, int64_t N, const R7Geometry& g,
+            int schedule, int cta_group, CUtensorMap* ma, CUtensorMap* mb, CMaps* mc,
+            GemmParams* p) {
+  const int tile_m = kBM * cta_group;
+  if (int e = make_map(ma, a_planes, g.k2p, scheme->rank * g.m2, ld_a, kBM, "A planes")) return e;
+  if (int e = make_map(mb, b_planes, g.k2p, scheme->rank * g.n2, ld_b, kBN / cta_group, "B planes"))
+    return e;
+  for (int bi = 0; bi < 2; ++bi)
+    for (int bj = 0; bj < 2; ++bj) {
+      const int64_t rows = bi == 0 ? g.m2 : M - g.m2;
+      const int64_t cols = bj == 0 ? g.n2 : N - g.n2;
+      const __nv_bfloat16* blk =
+          static_cast<const __nv_bfloat16*>(c) + bi * g.m2 * ldc + bj * g.n2;
+      if (int e = make_map(&mc->m[bi * 2 + bj], blk, cols, rows, ldc, kBM, "C block")) return e;
+    }
+  std::memset(p, 0, sizeof(*p));
+  const bool split = schedule == LCG_SCHEDULE_RANK_SPLIT;
+  for (int t = 0; t < scheme->rank; ++t) p->steps[t] = split ? scheme->rank_split[t] : scheme->all_ranks[t];
+  p->steps_per_unit = split ? 1 : scheme->rank;
+  p->rank_split = split ? 1 : 0;
+  p->tiles_m = static_cast<int>((g.m2 + tile_m - 1) / tile_m);
+  p->tiles_n = static_cast<int>((g.n2 + kBN - 1) / kBN);
+  p->group_m = pick_group_m(p->tiles_m, sm_count() / cta_group);
+  p->num_units = p->tiles_m * p->tiles_n * (split ? scheme->rank : 1);
+  p->k_blocks = static_cast<int>(g.k2p / kBK);
+  p->a_plane_rows = static_cast<int>(g.m2);
+  p->b_plane_rows = static_cast<int>(g.n2);
+  return LCG_OK;
+}
+
+}  // namespace
+}  // namespace lcg
+
+using namespace lcg;
+
+extern "C" int lcg_gemm_dense(const void* a, int64_t lda, const void* b, int64_t ldb, void* c,
+                              int64_t ldc, int64_t M, int64_t N, int64_t K, int cta_group,
+                              int32_t* status, void* stream) {
+  if (!a || !b || !c) return fail(LCG_ERR_BAD_ARG, "NULL operand");
+  if (M < 1 || N < 1 || K < 8 || K % 8 != 0)
+    return fail(LCG_ERR_UNSUPPORTED_SHAPE, "dense GEMM needs K %% 8 == 0, got M=%lld N=%lld K=%lld",
+                (long long)M, (long long)N, (long long)K);
+  if (lda < K || ldb < K || ldc < N) return fail(LCG_ERR_BAD_ARG, "leading dimension below extent");
+  cta_group = resolve_group(cta_group);
+  if (cta_group != 1 && cta_group != 2) return fail(LCG_ERR_BAD_ARG, "cta_group must be 0, 1 or 2");
+  CUtensorMap ma, mb;
+  CMaps mc;
+  if (int e = make_map(&ma, a, K, M, lda, kBM, "A")) return e;
+  if (int e = make_map(&mb, b, K, N, ldb, kBN / cta_group, "B")) return e;
+  if (int e = make_map(&mc.m[0], c, N, M, ldc, kBM, "C")) return e;
+  mc.m[1] = mc.m[2] = mc.m[3] = mc.m[0];
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  StepDesc& st = p.steps[0];
+  st.clear = 1;
+  st.ngroups = 1;
+  st.group[0].coeff = 1;
+  st.group[0].ndest = 1;
+  st.group[0].dest[0].first = 1;
+  const int tile_m = kBM * cta_group;
+  p.steps_per_unit = 1;
+  p.tiles_m = static_cast<int>((M + tile_m - 1) / tile_m);
+  p.tiles_n = static_cast<int>((N + kBN - 1) / kBN);
+  p.group_m = pick_group_m(p.tiles_m, sm_count() / cta_group);
+  p.num_units = p.tiles_m * p.tiles_n;
+  p.k_blocks = static_cast<int>((K + kBK - 1) / kBK);
+  p.status = status;
+  auto st_ = static_cast<cudaStream_t>(stream);
+  return cta_group == 1 ? launch<1, false>(ma, mb, mc, p, st_) : launch<2, false>(ma, mb, mc, p, st_);
+}
+
+extern "C" int lcg_gemm_r7(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,
+                           const void* b_planes, int64_t ld_b, void* c, int64_t ldc, int64_t M,
+                           int64_t N, int64_t K, int schedule, int cta_group, int32_t* status,
+                           void* stream) {
+  if (!scheme || !a_planes || !b_planes || !c) return fail(LCG_ERR_BAD_ARG, "NULL operand");
+  if (schedule != LCG_SCHEDULE_ALL_RANKS && schedule != LCG_SCHEDULE_RANK_SPLIT)
+    return fail(LCG_ERR_BAD_ARG, "unknown schedule %d", schedule);
+  cta_group = resolve_group(cta_group);
+  if (cta_group != 1 && cta_group != 2) return fail(LCG_ERR_BAD_ARG, "cta_group must be 0, 1 or 2");
+  R7Geometry g;
+  if (int e = r7_geometry(M, N, K, &g)) return e;
+  if (ldc < N) return fail(LCG_ERR_BAD_ARG, "ldc below N");
+  if (ld_a < g.k2p || ld_b < g.k2p) return fail(LCG_ERR_BAD_ARG, "plane leading dimension below K2p");
+  CUtensorMap ma, mb;
+  CMaps mc;
+  GemmParams p;
+  if (int e = fill_r7(scheme, a_planes, ld_a, b_planes, ld_b, c, ldc, M, N, g, schedule, cta_group,
+                      &ma, &mb, &mc, &p))
+    return e;
+  p.status = status;
+  auto st_ = static_cast<cudaStream_t>(stream);
+  return cta_group == 1 ? launch<1, false>(ma, mb, mc, p, st_) : launch<2, false>(ma, mb, mc, p, st_);
+}
+
+extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_scheme,
+                                 const void* a_planes, int64_t ld_a, const void* b_planes,
+                                 int64_t ld_b, void* z, int64_t ldz, int64_t M, int64_t N, int64_t K,
+                                 void* down_planes, int64_t ld_planes, void* preclear,
+                                 int64_t preclear_bytes, int cta_group, int32_t* status,
+                                 void* stream) {
+  if (!scheme || !plane_scheme || !a_planes || !b_planes || !z || !down_planes)
+    return fail(LCG_ERR_BAD_ARG, "NULL operand");
+  cta_group = resolve_group(cta_group);
+  if (cta_group != 1 && cta_group != 2) return fail(LCG_ERR_BAD_ARG, "cta_group must be 0, 1 or 2");
+  if (M % 2 != 0 || N % 256 != 0 || K % 128 != 0)
+    return fail(LCG_ERR_UNSUPPORTED_SHAPE,
+                "chained gate_up needs an even M, N %% 256 == 0 (I %% 128 == 0) and K %% 128 == 0; "
+                "got M=%lld N=%lld K=%lld",
+                (long long)M, (long long)N, (long long)K);
+  R7Geometry g;
+  if (int e = r7_geometry(M, N, K, &g)) return e;
+  const int64_t inter = N / 2;
+  if (g.n2 != inter) return fail(LCG_ERR_UNSUPPORTED_SHAPE, "gate/up split does not fall on a block");
+  if (ldz < N || ld_planes < inter / 2 || ld_planes % 8 != 0)
+    return fail(LCG_ERR_BAD_ARG, "bad leading dimensions");
+  if (ld_a < g.k2p || ld_b < g.k2p) return fail(LCG_ERR_BAD_ARG, "plane leading dimension below K2p");
+  if ((reinterpret_cast<uintptr_t>(down_planes) & 15u) != 0)
+    return fail(LCG_ERR_MISALIGNED, "down planes must be 16-byte aligned");
+  if (preclear != nullptr &&
+      (preclear_bytes < 0 || preclear_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(preclear) & 15u) != 0))
+    return fail(LCG_ERR_MISALIGNED, "preclear region must be 16-byte aligned and sized");
+  CUtensorMap ma, mb;
+  CMaps mc;
+  GemmParams p;
+  if (int e = fill_r7(scheme, a_planes, ld_a, b_planes, ld_b, z, ldz, M, N, g, LCG_SCHEDULE_ALL_RANKS,
+                      cta_group, &ma, &mb, &mc, &p))
+    return e;
+  p.status = status;
+  ChainParams& ch = p.chain;
+  ch.z = static_cast<const __nv_bfloat16*>(z);
+  ch.ldz = ldz;
+  ch.planes = static_cast<__nv_bfloat16*>(down_planes);
+  ch.ld_planes = ld_planes;
+  ch.m2 = static_cast<int32_t>(g.m2);
+  ch.inter = static_cast<int32_t>(inter);
+  ch.plane_rank = plane_scheme->rank;
+  for (int r = 0; r < plane_scheme->rank; ++r)
+    for (int x = 0; x < 4; ++x) ch.plane_terms.coef[r][x] = plane_scheme->a[r][x];
+  ch.preclear = preclear_bytes > 0 ? static_cast<uint4*>(preclear) : nullptr;
+  ch.preclear_vecs = preclear_bytes / 16;
+  auto st_ = static_cast<cudaStream_t>(stream);
+  return cta_group == 1 ? launch<1, true>(ma, mb, mc, p, st_) : launch<2, true>(ma, mb, mc, p, st_);
+}
+
+extern "C" int lcg_describe_gemm(int64_t M, int64_t N, int64_t K, int rank7, int schedule,
+                                 int cta_group, char* buf, int buflen) {
+  if (buf == nullptr || buflen < 1) return fail(LCG_ERR_BAD_ARG, "no buffer");
+  cta_group = resolve_group(cta_group);
+  const int tile_m = kBM * cta_group;
+  const int stages = cta_group == 1 ? Tile<1>::kStages : Tile<2>::kStages;
+  const int smem = cta_group == 1 ? Tile<1>::kSmemBytes : Tile<2>::kSmemBytes;
+  int64_t rows = M, cols = N, kk = K;
+  int units_mul = 1;
+  if (rank7) {
+    R7Geometry g;
+    if (int e = r7_geometry(M, N, K, &g)) return e;
+    rows = g.m2;
+    cols = g.n2;
+    kk = g.k2p;
+    if (schedule == LCG_SCHEDULE_RANK_SPLIT) units_mul = 7;
+  }
+  const int64_t tm = (rows + tile_m - 1) / tile_m, tn = (cols + kBN - 1) / kBN;
+  const int groups = sm_count() / cta_group;
+  const int64_t units = tm * tn * units_mul;
+  return snprintf(buf, buflen,
+                  "%s %lldx%lldx%lld: tile %dx%dx%d cta_group=%d stages=%d smem=%dB tmem=512 cols (2 acc "
+                  "stages); %lldx%lld tiles, %lld units over %d CTA groups (%.2f waves), %lld k-blocks/step",
+                  rank7 ? (schedule == LCG_SCHEDULE_RANK_SPLIT ? "rank7/rank-split" : "rank7/all-ranks")
+                        : "dense",
+                  (long long)M, (long long)K, (long long)N, tile_m, kBN, kBK, cta_group, stages, smem,
+                  (long long)tm, (long long)tn, (long long)units, groups,
+                  static_cast<double>(units) / groups, (long long)((kk + kBK - 1) / kBK));
+}

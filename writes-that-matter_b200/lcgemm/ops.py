@@ -1,0 +1,246 @@
+"""Torch-tensor front end of the C ABI: argument checks, output allocation, status word.
+
+Every function here launches CUDA work on the current torch stream through
+``include/lcgemm_b200.h`` and never synchronises.  Tensors must be bf16 CUDA
+tensors; there is no CPU implementation behind these calls.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _native as nat
+from ._native import NativeScheme, check, lib, ptr, stream_ptr
+
+BF16 = torch.bfloat16
+
+_STATUS: dict = {}
+
+
+def _need(t: torch.Tensor, what: str, rows_contig: bool = True) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(
+            f"{what} must be a CUDA tensor: lcgemm_b200 has no CPU implementation of this path")
+    if t.dtype != BF16:
+        raise ValueError(f"{what} must be bfloat16, got {t.dtype}")
+    if rows_contig and t.dim() == 2 and t.stride(1) != 1:
+        raise ValueError(f"{what} must be row-major (unit stride along its last dimension)")
+
+
+def status_word(device=None) -> torch.Tensor:
+    """The per-device int32 word the tcgen05 kernels flag a run-out wait in."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _STATUS.get(dev)
+    if word is None:
+        word = _STATUS[dev] = torch.zeros(4, dtype=torch.int32, device=dev)
+    return word
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if any kernel since the last check gave up a wait."""
+    word = status_word(device)
+    code = int(word[0].item())
+    if code != 0:
+        word.zero_()
+        raise RuntimeError(
+            f"lcgemm_b200: a device-side wait ran out (code {code}: 101 producer, 102/103 MMA "
+            f"issuer, 104 epilogue, 105 plane warps); results of that launch are invalid")
+
+
+def launch_count() -> int:
+    return int(lib().lcg_launch_count())
+
+
+def describe_gemm(m: int, n: int, k: int, rank7: bool = True, schedule: int = 0,
+                  cta_group: int = 0) -> str:
+    buf = ctypes.create_string_buffer(512)
+    got = lib().lcg_describe_gemm(m, n, k, int(rank7), schedule, cta_group, buf, 512)
+    if got < 0:
+        check(got)
+    return buf.value.decode()
+
+
+# ------------------------------------------------------------------ geometry
+def a_plane_shape(scheme, m: int, k: int):
+    m2, _, k2p = nat.plane_geometry(m, k, 1)
+    return scheme.rank * m2, k2p
+
+
+def b_plane_shape(scheme, n: int, k: int):
+    n2, _, k2p = nat.plane_geometry(n, k, 8)
+    return scheme.rank * n2, k2p
+
+
+# -------------------------------------------------------------------- planes
+def prepare_b(w: torch.Tensor, scheme) -> torch.Tensor:
+    """B planes ``(rank * N2, K2p)`` of a weight ``(N, K)``."""
+    _need(w, "weight")
+    n, k = w.shape
+    out = torch.empty(b_plane_shape(scheme, n, k), dtype=BF16, device=w.device)
+    check(lib().lcg_prepare_b(NativeScheme.of(scheme).handle, ptr(w), n, k, w.stride(0), ptr(out),
+                              out.stride(0), stream_ptr()))
+    return out
+
+
+def a_planes(a: torch.Tensor, scheme, out: torch.Tensor | None = None) -> torch.Tensor:
+    """A planes ``(rank * M2, K2p)`` of a plain activation matrix ``(M, K)``."""
+    _need(a, "activation")
+    m, k = a.shape
+    shape = a_plane_shape(scheme, m, k)
+    if out is None:
+        out = torch.empty(shape, dtype=BF16, device=a.device)
+    elif tuple(out.shape) != shape:
+        raise ValueError(f"A-plane buffer must be {shape}, got {tuple(out.shape)}")
+    check(lib().lcg_a_planes(NativeScheme.of(scheme).handle, ptr(a), m, k, a.stride(0), ptr(out),
+                             out.stride(0), stream_ptr()))
+    return out
+
+
+def norm_planes(scheme, delta, residual, norm_weight, eps: float, residual_out, out) -> None:
+    for t, what in ((delta, "delta"), (residual, "residual"), (norm_weight, "norm weight"),
+                    (residual_out, "residual_out"), (out, "A planes")):
+        _need(t, what)
+    m, k = delta.shape
+    for t, what in ((delta, "delta"), (residual, "residual"), (residual_out, "residual_out")):
+        if tuple(t.shape) != (m, k) or not t.is_contiguous():
+            raise ValueError(f"{what} must be a contiguous ({m}, {k}) tensor")
+    if tuple(norm_weight.shape) != (k,):
+        raise ValueError(f"norm weight must be ({k},)")
+    if tuple(out.shape) != a_plane_shape(scheme, m, k):
+        raise ValueError(f"A workspace must be {a_plane_shape(scheme, m, k)}, got {tuple(out.shape)}")
+    check(lib().lcg_norm_planes(NativeScheme.of(scheme).handle, ptr(delta), ptr(residual),
+                                ptr(norm_weight), m, k, float(eps), ptr(residual_out), ptr(out),
+                                out.stride(0), stream_ptr()))
+
+
+def swiglu_planes(plane_scheme, z: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``L_r(silu(z[:, :I]) * z[:, I:])`` in the interleaved gauge, ``(rank * M/2, I/2)``."""
+    _need(z, "z")
+    m, two_i = z.shape
+    inter = two_i // 2
+    shape = (plane_scheme.rank * (m // 2), inter // 2)
+    if out is None:
+        out = torch.empty(shape, dtype=BF16, device=z.device)
+    elif tuple(out.shape) != shape:
+        raise ValueError(f"plane buffer must be {shape}, got {tuple(out.shape)}")
+    check(lib().lcg_swiglu_planes(NativeScheme.of(plane_scheme).handle, ptr(z), m, inter,
+                                  z.stride(0), ptr(out), out.stride(0), stream_ptr()))
+    return out
+
+
+# --------------------------------------------------------------------- GEMMs
+def _padded_out(m: int, n: int, device) -> torch.Tensor:
+    """An (m, n) view whose row pitch is a multiple of 8 elements (TMA store needs 16 bytes)."""
+    ld = (n + 7) // 8 * 8
+    return torch.empty((m, ld), dtype=BF16, device=device)[:, :n]
+
+
+def gemm_dense(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
+               cta_group: int = 0) -> torch.Tensor:
+    """``a @ b.T`` with ``a (M, K)``, ``b (N, K)`` on the dense tcgen05 kernel."""
+    _need(a, "a"), _need(b, "b")
+    m, k = a.shape
+    n, kb = b.shape
+    if kb != k:
+        raise ValueError(f"inner dimensions differ: {k} vs {kb}")
+    if out is None:
+        out = _padded_out(m, n, a.device)
+    _need(out, "out")
+    check(lib().lcg_gemm_dense(ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(out), out.stride(0),
+                               m, n, k, cta_group, ptr(status_word(a.device)), stream_ptr()))
+    return out
+
+
+def gemm_r7_planes(scheme, a_pl: torch.Tensor, b_pl: torch.Tensor, m: int, n: int, k: int,
+                   out: torch.Tensor | None = None, schedule: int = nat.SCHEDULE_ALL_RANKS,
+                   cta_group: int = 0, zero_out: bool = True) -> torch.Tensor:
+    """Rank-7 ``C = A @ B^T`` from prepared planes.  With the rank-split schedule the output
+    must arrive zeroed; ``zero_out`` does that here with a memset on the stream."""
+    _need(a_pl, "A planes"), _need(b_pl, "B planes")
+    if tuple(a_pl.shape) != a_plane_shape(scheme, m, k):
+        raise ValueError(f"A planes must be {a_plane_shape(scheme, m, k)}, got {tuple(a_pl.shape)}")
+    if tuple(b_pl.shape) != b_plane_shape(scheme, n, k):
+        raise ValueError(f"B planes must be {b_plane_shape(scheme, n, k)}, got {tuple(b_pl.shape)}")
+    if out is None:
+        out = _padded_out(m, n, a_pl.device)
+    _need(out, "out")
+    if tuple(out.shape) != (m, n):
+        raise ValueError(f"out must be ({m}, {n}), got {tuple(out.shape)}")
+    if schedule == nat.SCHEDULE_RANK_SPLIT and zero_out:
+        out.zero_()
+    check(lib().lcg_gemm_r7(NativeScheme.of(scheme).handle, ptr(a_pl), a_pl.stride(0), ptr(b_pl),
+                            b_pl.stride(0), ptr(out), out.stride(0), m, n, k, schedule, cta_group,
+                            ptr(status_word(a_pl.device)), stream_ptr()))
+    return out
+
+
+def gemm_r7(a: torch.Tensor, b_pl: torch.Tensor, n: int, scheme, out: torch.Tensor | None = None,
+            a_workspace: torch.Tensor | None = None, schedule: int = nat.SCHEDULE_ALL_RANKS,
+            cta_group: int = 0) -> torch.Tensor:
+    """Bare rank-7 GEMM: form the A planes of ``a (M, K)``, then multiply with prepared B planes."""
+    m, k = a.shape
+    planes = a_planes(a, scheme, out=a_workspace)
+    return gemm_r7_planes(scheme, planes, b_pl, m, n, k, out=out, schedule=schedule,
+                          cta_group=cta_group)
+
+
+def gate_up_chain(scheme, plane_scheme, a_pl, b_pl, z, down_planes, preclear=None,
+                  cta_group: int = 0) -> None:
+    for t, what in ((a_pl, "A planes"), (b_pl, "B planes"), (z, "z"), (down_planes, "down planes")):
+        _need(t, what)
+    m, n = z.shape
+    k = 2 * a_pl.shape[1]
+    if tuple(a_pl.shape) != a_plane_shape(scheme, m, k) or tuple(b_pl.shape) != b_plane_shape(scheme, n, k):
+        raise ValueError("operand planes do not match the output shape")
+    if tuple(down_planes.shape) != (plane_scheme.rank * (m // 2), n // 4):
+        raise ValueError(
+            f"down planes must be ({plane_scheme.rank * (m // 2)}, {n // 4}), got {tuple(down_planes.shape)}")
+    pc_ptr, pc_bytes = 0, 0
+    if preclear is not None:
+        _need(preclear, "preclear")
+        if not preclear.is_contiguous():
+            raise ValueError("the consumer output to clear must be contiguous")
+        pc_ptr, pc_bytes = ptr(preclear), preclear.numel() * preclear.element_size()
+    check(lib().lcg_gate_up_chain(NativeScheme.of(scheme).handle, NativeScheme.of(plane_scheme).handle,
+                                  ptr(a_pl), a_pl.stride(0), ptr(b_pl), b_pl.stride(0), ptr(z),
+                                  z.stride(0), m, n, k, ptr(down_planes), down_planes.stride(0),
+                                  pc_ptr, pc_bytes, cta_group, ptr(status_word(z.device)),
+                                  stream_ptr()))
+
+
+# -------------------------------------------------------------- dense seams
+def add_rmsnorm(delta, residual, norm_weight, eps: float, residual_out=None, x=None):
+    for t, what in ((delta, "delta"), (residual, "residual"), (norm_weight, "norm weight")):
+        _need(t, what)
+    m, k = delta.shape
+    if residual_out is None:
+        residual_out = torch.empty_like(delta)
+    if x is None:
+        x = torch.empty_like(delta)
+    for t in (delta, residual, residual_out, x):
+        if tuple(t.shape) != (m, k) or not t.is_contiguous():
+            raise ValueError(f"operands must be contiguous ({m}, {k}) tensors")
+    check(lib().lcg_add_rmsnorm(ptr(delta), ptr(residual), ptr(norm_weight), m, k, float(eps),
+                                ptr(residual_out), ptr(x), stream_ptr()))
+    return x, residual_out
+
+
+def swiglu(z: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    _need(z, "z")
+    m, two_i = z.shape
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty((m, inter), dtype=BF16, device=z.device)
+    check(lib().lcg_swiglu(ptr(z), m, inter, z.stride(0), ptr(out), out.stride(0), stream_ptr()))
+    return out
+
+
+def add(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    _need(a, "a"), _need(b, "b")
+    if a.shape != b.shape or not a.is_contiguous() or not b.is_contiguous():
+        raise ValueError("operands must be contiguous and of equal shape")
+    if out is None:
+        out = torch.empty_like(a)
+    check(lib().lcg_add(ptr(a), ptr(b), ptr(out), a.numel(), stream_ptr()))
+    return out
