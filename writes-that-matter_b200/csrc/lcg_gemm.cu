@@ -408,20 +408,13 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
             float o[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) o[e] = 0.f;
-            bool started = false;
 #pragma unroll
             for (int x = 0; x < 4; ++x) {
               const int cf = ch.plane_terms.coef[r][x];
               if (cf == 0) continue;
               const float w = static_cast<float>(cf);
-              if (!started) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = w * sv[x][e];
-                started = true;
-              } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = fmaf(w, sv[x][e], o[e]);
-              }
+              for (int e = 0; e < 8; ++e) o[e] = fmaf(w, sv[x][e], o[e]);
             }
             uint4 outv;
             outv.x = pack_bf16x2(o[0], o[1]);

@@ -60,22 +60,17 @@ __device__ __forceinline__ void load8_guarded(const __nv_bfloat16* __restrict__ 
 
 __device__ __forceinline__ void signed_sum(const TermTable& tt, int r, const float (&blk)[4][8],
                                            float (&out)[8]) {
+  // Starts from +0 and adds term by term in block order, so a sum of zeros is +0 whatever
+  // the signs of the coefficients (a bare -1 * 0 would be -0).
 #pragma unroll
   for (int t = 0; t < 8; ++t) out[t] = 0.f;
-  bool started = false;
 #pragma unroll
   for (int x = 0; x < 4; ++x) {
     const int cf = tt.coef[r][x];
     if (cf == 0) continue;
     const float w = static_cast<float>(cf);
-    if (!started) {
 #pragma unroll
-      for (int t = 0; t < 8; ++t) out[t] = w * blk[x][t];
-      started = true;
-    } else {
-#pragma unroll
-      for (int t = 0; t < 8; ++t) out[t] = fmaf(w, blk[x][t], out[t]);
-    }
+    for (int t = 0; t < 8; ++t) out[t] = fmaf(w, blk[x][t], out[t]);
   }
 }
 

@@ -1,0 +1,95 @@
+"""One dense-decoder MLP layer in three arms, for the single-layer configuration
+``x -> RMSNorm -> gate_up -> SwiGLU -> down -> + residual`` and as the building block of the
+tensor-parallel form.
+
+* :class:`Rank7MlpLayer`  the rank-7 chain: fused norm planes, chained gate_up GEMM, down GEMM
+  (what ``lcgemm_qwen::mlp_chain`` runs, ``lcgemm/integrate/qwen_patch.py:85-97``), 3 launches
+  plus the closing residual add;
+* :class:`DenseMlpLayer`  the stock layer (``lcgemm/integrate/qwen_patch.py:41-58``) on the
+  dense tcgen05 GEMM of this library, or on cuBLAS through ``torch.matmul`` with
+  ``gemm="cublas"``: norm, GEMM, SwiGLU, GEMM, residual add.
+
+Both keep the layer's output buffers and return views of them.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+from .seams import build_chain
+
+
+class Rank7MlpLayer:
+    def __init__(self, tokens: int, norm_weight, gate_up_weight, down_weight, eps: float = 1e-6,
+                 cta_group: int = 0):
+        two_i, hidden = gate_up_weight.shape
+        out_dim, inter = down_weight.shape
+        if two_i != 2 * inter:
+            raise ValueError("gate_up weight must have 2 * intermediate rows")
+        self.eps = eps
+        self.norm_weight = norm_weight
+        self.gate_plan, self.down_plan = build_chain((tokens, hidden, two_i), (tokens, inter, out_dim))
+        self.gate_plan.cta_group = self.down_plan.cta_group = cta_group
+        self.gate_bw = self.gate_plan.prepare_weight(gate_up_weight)
+        self.down_bw = self.down_plan.prepare_weight(down_weight)
+        self.out = torch.empty((tokens, out_dim), device=gate_up_weight.device, dtype=torch.bfloat16)
+        self._zero = None
+
+    def chain(self, delta, residual):
+        """``(down_out, residual_out)`` exactly as the custom op returns them."""
+        self.gate_plan(residual, delta, self.norm_weight, self.eps, prepared_w=self.gate_bw)
+        return self.down_plan(prepared_w=self.down_bw), self.gate_plan.residual_out
+
+    def forward(self, x, delta=None):
+        """``h + mlp(norm(h))`` with ``h = x + delta`` (``delta`` defaults to zero)."""
+        if delta is None:
+            if self._zero is None or self._zero.shape != x.shape:
+                self._zero = torch.zeros_like(x)
+            delta = self._zero
+        down_out, h = self.chain(delta, x)
+        return ops.add(h, down_out if down_out.is_contiguous() else down_out.contiguous(), out=self.out)
+
+    __call__ = forward
+    launches_per_forward = 4
+
+
+class DenseMlpLayer:
+    def __init__(self, tokens: int, norm_weight, gate_up_weight, down_weight, eps: float = 1e-6,
+                 gemm: str = "tcgen05", cta_group: int = 0):
+        if gemm not in ("tcgen05", "cublas"):
+            raise ValueError("gemm must be 'tcgen05' or 'cublas'")
+        two_i, hidden = gate_up_weight.shape
+        out_dim, inter = down_weight.shape
+        dev, bf = gate_up_weight.device, torch.bfloat16
+        self.eps, self.gemm, self.cta_group = eps, gemm, cta_group
+        self.norm_weight, self.w_gu, self.w_down = norm_weight, gate_up_weight, down_weight
+        self.h = torch.empty((tokens, hidden), device=dev, dtype=bf)
+        self.x = torch.empty((tokens, hidden), device=dev, dtype=bf)
+        self.z = torch.empty((tokens, two_i), device=dev, dtype=bf)
+        self.s = torch.empty((tokens, inter), device=dev, dtype=bf)
+        self.d = torch.empty((tokens, out_dim), device=dev, dtype=bf)
+        self.out = torch.empty((tokens, out_dim), device=dev, dtype=bf)
+        self._zero = None
+
+    def _mm(self, a, w, out):
+        if self.gemm == "cublas":
+            return torch.matmul(a, w.t(), out=out)
+        return ops.gemm_dense(a, w, out=out, cta_group=self.cta_group)
+
+    def chain(self, delta, residual):
+        ops.add_rmsnorm(delta, residual, self.norm_weight, self.eps, residual_out=self.h, x=self.x)
+        self._mm(self.x, self.w_gu, self.z)
+        ops.swiglu(self.z, out=self.s)
+        self._mm(self.s, self.w_down, self.d)
+        return self.d, self.h
+
+    def forward(self, x, delta=None):
+        if delta is None:
+            if self._zero is None or self._zero.shape != x.shape:
+                self._zero = torch.zeros_like(x)
+            delta = self._zero
+        d, h = self.chain(delta, x)
+        return ops.add(h, d, out=self.out)
+
+    __call__ = forward
+    launches_per_forward = 5

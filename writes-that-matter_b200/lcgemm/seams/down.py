@@ -1,0 +1,92 @@
+"""The chained ``down`` seam: a plane-consuming rank-7 GEMM (``lcgemm/seams/down.py``).
+
+    S = silu(Z[:, :I]) * Z[:, I:]        # never lands in HBM as such
+    out = S @ W_down^T
+
+The ``gate_up`` epilogue has already applied SwiGLU and written the A planes, so this seam
+launches only the GEMM.  Its static weight is permuted into the interleaved-K gauge once,
+at installation.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import chain_gauge, ops
+from .._native import SCHEDULE_ALL_RANKS, SCHEDULE_RANK_SPLIT
+from ..scheme import Scheme
+
+# Shapes the reference runs rank-split (lcgemm/seams/down.py:42-54); kept as the validated set.
+RANK_SPLIT_SHAPES = {
+    (512, 19968, 6656), (512, 17408, 5120), (1024, 19968, 6656), (1024, 17408, 5120),
+    (2048, 19968, 6656), (2048, 17408, 5120), (4096, 17408, 5120), (8192, 17408, 5120),
+}
+
+_CTA_GROUPS = 74            # 2-CTA groups resident on a 148-SM B200
+_SPLIT_PENALTY = 0.97       # reduce-add scatter and pre-zeroing cost of the rank-split form
+
+
+def wants_rank_split(shape) -> bool:
+    """Whether the product index has to carry parallelism: compare the wave-quantisation
+    efficiency of ``tiles`` units against ``7 * tiles`` units on the resident CTA groups."""
+    if tuple(shape) in RANK_SPLIT_SHAPES:
+        return True
+    m, _, n = shape
+    tiles = math.ceil((m + 1) // 2 / 256) * math.ceil(((n + 1) // 2) / 256)
+    eff = lambda units: units / (math.ceil(units / _CTA_GROUPS) * _CTA_GROUPS)
+    return eff(7 * tiles) * _SPLIT_PENALTY > eff(tiles)
+
+
+class DownPlan:
+    """The ``down`` plan, coupled to its ``gate_up`` producer."""
+
+    seam = "down"
+
+    def __init__(self, scheme: Scheme, shape, *, producer, cta_group: int = 0):
+        m, k, n = shape
+        if k % 128:
+            raise ValueError(f"down shape {tuple(shape)}: K must be a multiple of 128 (the gauge width)")
+        self.scheme = scheme
+        self.shape = tuple(shape)                       # (M, K, N)
+        self.producer = producer
+        self.cta_group = cta_group
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self._store = torch.empty((m, (n + 7) // 8 * 8), device=dev, dtype=torch.bfloat16)
+        self.c = self._store[:, :n] if n % 8 else self._store
+        self.rank_split = wants_rank_split(self.shape)
+        self._desc = None
+
+    # ---------------------------------------------------------------- offline
+    def prepare_weight(self, w: torch.Tensor) -> torch.Tensor:
+        """The R combined B planes with the K permutation of the gauge folded in."""
+        return chain_gauge.prepare_down_b(w, self.scheme, chain_gauge.CHUNK)
+
+    # ------------------------------------------------------------------ parts
+    def a_planes(self) -> torch.Tensor:
+        """The planes already produced by the chained gate/up epilogue."""
+        return self.producer.planes
+
+    def gemm(self, a_planes, prepared_w, *, out=None) -> torch.Tensor:
+        c = self.c if out is None else out
+        m, k, n = self.shape
+        # A rank-split output must arrive zeroed.  The chained producer does that for ``self.c``
+        # while it runs; any other destination is cleared here.
+        cleared_by_producer = (self.producer is not None and c is self.c
+                               and getattr(self.producer, "preclear", None) is self.c)
+        ops.gemm_r7_planes(
+            self.scheme, a_planes, prepared_w, m, n, k, out=c,
+            schedule=SCHEDULE_RANK_SPLIT if self.rank_split else SCHEDULE_ALL_RANKS,
+            cta_group=self.cta_group, zero_out=self.rank_split and not cleared_by_producer)
+        return c
+
+    def __call__(self, *, prepared_w, out=None):
+        return self.gemm(self.a_planes(), prepared_w, out=out)
+
+    def describe(self) -> str:
+        if self._desc is None:
+            m, k, n = self.shape
+            self._desc = "  chained (a_planes are free)\n" + ops.describe_gemm(
+                m, n, k, True, SCHEDULE_RANK_SPLIT if self.rank_split else SCHEDULE_ALL_RANKS,
+                self.cta_group)
+        return self._desc

@@ -1,0 +1,81 @@
+"""Tensor-parallel MLP over the intermediate dimension (2 / 4 / 8 GPUs of one node).
+
+The reference enforces TP = 1 (``lcgemm/integrate/qwen_patch.py:216-217``); this is the
+multi-GPU form of the same layer.  Rank ``g`` of ``tp`` holds
+
+* ``gate_up`` shard ``[W_gate[g*I/tp:(g+1)*I/tp]; W_up[g*I/tp:(g+1)*I/tp]]`` -- column
+  parallel, and still ``[gate | up]`` halves, which is what the chained kernel's SwiGLU
+  epilogue needs (``lcgemm/kernels/sm100.py:239-241``);
+* ``down`` shard ``W_down[:, g*I/tp:(g+1)*I/tp]`` -- row parallel.
+
+Each rank runs the whole rank-7 chain on its shard with no communication (the input is
+replicated), producing a partial ``(M, H)`` output; one all-reduce (NCCL over
+NVLink/NVSwitch, bf16 sum) per layer combines the partials, and the residual is added after
+the reduction.  One process per GPU; ``torch.distributed`` provides the process group.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def shard_mlp_weights(gate_up_weight: torch.Tensor, down_weight: torch.Tensor, rank: int, world: int):
+    """The ``(gate_up_shard, down_shard)`` of one rank from full weights ``(2I, H)``, ``(H, I)``."""
+    two_i = gate_up_weight.shape[0]
+    inter = two_i // 2
+    if two_i % 2 or inter % world or down_weight.shape[1] != inter:
+        raise ValueError(f"intermediate size {inter} does not split over {world} ranks")
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside [0, {world})")
+    per = inter // world
+    lo, hi = rank * per, (rank + 1) * per
+    gate_up = torch.cat([gate_up_weight[lo:hi], gate_up_weight[inter + lo:inter + hi]], dim=0)
+    return gate_up.contiguous(), down_weight[:, lo:hi].contiguous()
+
+
+def all_reduce_sum(t: torch.Tensor, group=None) -> torch.Tensor:
+    """In-place sum over the group; a no-op without an initialised group or with one rank."""
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+    return t
+
+
+class TensorParallelMlp:
+    """``h + all_reduce(down_g(SwiGLU(gate_up_g(norm(h)))))`` with ``h = x + delta``.
+
+    ``make_layer(tokens, norm_weight, gate_up_shard, down_shard, eps)`` builds the per-rank
+    layer; it must offer ``chain(delta, residual) -> (partial, h)``.  The default is the
+    rank-7 chain of this package; tests pass a CPU stand-in to drive the same control flow
+    over a ``gloo`` group.
+    """
+
+    def __init__(self, tokens: int, norm_weight, gate_up_shard, down_shard, eps: float = 1e-6,
+                 group=None, make_layer=None, add=None):
+        if make_layer is None:
+            from .layer import Rank7MlpLayer as make_layer
+        self.group = group
+        self.layer = make_layer(tokens, norm_weight, gate_up_shard, down_shard, eps)
+        self._add = add
+        self._zero = None
+        self.out = None
+
+    def forward(self, x: torch.Tensor, delta: torch.Tensor | None = None) -> torch.Tensor:
+        if delta is None:
+            if self._zero is None or self._zero.shape != x.shape:
+                self._zero = torch.zeros_like(x)
+            delta = self._zero
+        partial, h = self.layer.chain(delta, x)
+        if not partial.is_contiguous():
+            partial = partial.contiguous()
+        all_reduce_sum(partial, self.group)
+        if self._add is not None:
+            self.out = self._add(h, partial)
+        else:
+            from . import ops
+
+            if self.out is None or self.out.shape != h.shape:
+                self.out = torch.empty_like(h)
+            ops.add(h, partial, out=self.out)
+        return self.out
+
+    __call__ = forward
