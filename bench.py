@@ -1,0 +1,470 @@
+#!/usr/bin/env python
+"""Benchmark of the rank-7 MLP prefill path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Metric (BASELINE.json): MLP prefill effective TFLOP/s (6*M*H*I / time for one layer:
+gate_up + down, dense-equivalent FLOPs) and % speedup over the dense bf16 path.
+
+N = 1   one "step" = one fused MLP layer of the single-layer configuration
+        (4096 tokens x hidden 5120, intermediate 17408): fused residual+RMSNorm+A planes,
+        chained rank-7 gate_up GEMM (SwiGLU + down's A planes in its epilogue), rank-split
+        rank-7 down GEMM, residual add.  The dense arms (own tcgen05 GEMM, cuBLAS) run
+        interleaved in the same process for the speedup figures, and 2048 / 8192 tokens are
+        measured beside the headline 4096.
+N > 1   the tensor-parallel configuration (8192 tokens, hidden 8192, intermediate 28672)
+        split over the intermediate dimension, one NCCL all-reduce per layer; total work is
+        fixed as N grows ("strong" scaling).  One process per GPU under torchrun.
+
+Timing: CUDA events on the launching stream around every step, L2 flushed (256 MiB memset)
+between steps outside the timed region, max over ranks.  `e2e` repeats the measurement
+through the public layer call with the step's input in pinned host memory and the result
+read back to the host inside the timed region.
+
+--impl reference times the CPU evaluation of the same scheme (the oracle port of the
+reference's torch functions) on the host cores, on a bounded row sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (str(ROOT / "writes-that-matter_b200"), str(ROOT)):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+METRIC = "MLP prefill effective TFLOP/s (6*M*H*I/t per layer) & % speedup vs dense bf16"
+SINGLE = dict(tokens=4096, hidden=5120, inter=17408)
+TP = dict(tokens=8192, hidden=8192, inter=28672)
+EPS = 1e-6
+CPU_SAMPLE_TOKENS = 256
+FLUSH_BYTES = 256 << 20
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate_up launch at the headline shape,
+# from the ncu capture summarised in profiles/; None until a capture exists.
+GATE_UP_DRAM_TRAFFIC_BYTES = None
+
+
+def layer_flops(tokens, hidden, inter):
+    return 6.0 * tokens * hidden * inter
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
+# ------------------------------------------------------------------ clock sampling
+class ClockWatch:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap",
+               0x8: "hw_slowdown", 0x10: "sync_boost", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x100: "display_clock"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit and name != "gpu_idle":
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.004)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------ synthetic data
+def make_layer_tensors(tokens, hidden, inter, device, seed=0, inter_local=None, rank=0):
+    """Seeded synthetic tensors with the distributions BASELINE.json names: x ~ N(0,1),
+    norm weight stored as w with effective scale 1 + w, w ~ N(0, 0.01), weights ~ N(0, 0.02)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    bf = torch.bfloat16
+    x = torch.randn((tokens, hidden), generator=g, device=device).to(bf)
+    nw = (torch.randn((hidden,), generator=g, device=device) * 0.01).to(bf)
+    gw = torch.Generator(device=device).manual_seed(seed + 1000 + rank)
+    il = inter if inter_local is None else inter_local
+    wgu = (torch.randn((2 * il, hidden), generator=gw, device=device) * 0.02).to(bf)
+    wd = (torch.randn((hidden, il), generator=gw, device=device) * 0.02).to(bf)
+    return x, nw, wgu, wd
+
+
+# ------------------------------------------------------------------------- timing
+def timed_steps(step_fn, steps, warmup, flush, sync_all, pre_step=None):
+    """Per-step CUDA-event times (ms).  `flush` is zeroed between steps, outside the events."""
+    for _ in range(warmup):
+        if pre_step:
+            pre_step()
+        step_fn()
+    sync_all()
+    times = []
+    for _ in range(steps):
+        flush.zero_()
+        if pre_step:
+            pre_step()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step_fn()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    sync_all()
+    return times
+
+
+def run_cpu_sample(tokens, hidden, inter, threads=None):
+    """The oracle's chained rank-7 layer on a row sample, host cores; returns (seconds, flops)."""
+    from oracle import lc_oracle as O
+
+    if threads:
+        torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    bf = torch.bfloat16
+    x = torch.randn((tokens, hidden), generator=g).to(bf)
+    nw = (torch.randn((hidden,), generator=g) * 0.01).to(bf)
+    wgu = (torch.randn((2 * inter, hidden), generator=g) * 0.02).to(bf)
+    wd = (torch.randn((hidden, inter), generator=g) * 0.02).to(bf)
+    gt, dt = O.Tables("2x2_postsum_cse"), O.Tables("2x2_locality_ordered")
+    gate_b = O.prepare_b(wgu, gt).float()          # offline in the reference: not timed
+    down_b = O.prepare_down_b(wd, dt).float()
+    zero = torch.zeros_like(x)
+
+    def step():
+        a_pl, h = O.norm_planes(zero, x, nw, EPS, gt)
+        prods = O.products(a_pl, gate_b, gt.rank)
+        z = O.combine_as_kernel(prods, gt, tokens, 2 * inter).to(bf)
+        d_pl = O.chain_a_planes(z, dt)
+        prods = O.products(d_pl, down_b, dt.rank)
+        out = O.combine_as_kernel(prods, dt, tokens, hidden, rank_split=True)
+        return (h.float() + out).to(bf)
+
+    return step, layer_flops(tokens, hidden, inter)
+
+
+def cpu_baseline(hidden, inter, reps=3):
+    step, flops = run_cpu_sample(CPU_SAMPLE_TOKENS, hidden, inter)
+    step()
+    best = min(_wall(step) for _ in range(reps))
+    return {"value": flops / best / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": f"{CPU_SAMPLE_TOKENS} of the tokens, full hidden {hidden} / intermediate {inter}; "
+                      f"oracle chained rank-7 layer (torch fp32 matmul on bf16-rounded planes), "
+                      f"B planes prepared untimed, best of {reps}, {best * 1e3:.1f} ms"}
+
+
+def _wall(fn):
+    t0 = time.perf_counter()
+    fn()
+    return time.perf_counter() - t0
+
+
+# ------------------------------------------------------------------ reference arm
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    cfg = SINGLE if args.gpus == 1 else TP
+    step, flops = run_cpu_sample(CPU_SAMPLE_TOKENS, cfg["hidden"], cfg["inter"])
+    for _ in range(min(args.warmup, 2)):
+        step()
+    steps = max(1, min(args.steps, 100))
+    times = [_wall(step) for _ in range(steps)]
+    ms = statistics.mean(times) * 1e3
+    val = flops / (ms * 1e-3) / 1e12
+    sample = (f"{CPU_SAMPLE_TOKENS}-token row sample of the {cfg['tokens']}-token layer per step, "
+              f"{steps} timed steps, oracle port of the reference's torch scheme "
+              f"evaluation on the host cores")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": _workload_name(args.gpus), **cfg, "cpu_sample_tokens": CPU_SAMPLE_TOKENS},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def _workload_name(gpus):
+    if gpus == 1:
+        return "single fused MLP layer, 4096 tokens x 5120, intermediate 17408 (BASELINE config 2)"
+    return f"tensor-parallel MLP tp={gpus}, 8192 tokens x 8192, intermediate 28672 (BASELINE config 4)"
+
+
+# --------------------------------------------------------------------- our arm
+def bench_layer_arms(tokens, hidden, inter, steps, warmup, flush, device, with_parts=False):
+    """Rank-7 layer and the two dense arms, interleaved step by step.  Returns a dict of
+    median / mean ms per arm, and (optionally) the gate_up GEMM's own duration."""
+    from lcgemm import ops
+    from lcgemm.layer import DenseMlpLayer, Rank7MlpLayer
+
+    x, nw, wgu, wd = make_layer_tensors(tokens, hidden, inter, device)
+    r7 = Rank7MlpLayer(tokens, nw, wgu, wd, EPS)
+    dn = DenseMlpLayer(tokens, nw, wgu, wd, EPS, gemm="tcgen05")
+    cb = DenseMlpLayer(tokens, nw, wgu, wd, EPS, gemm="cublas")
+    zero = torch.zeros_like(x)
+    part_events = []
+
+    def r7_step():
+        gp, dp = r7.gate_plan, r7.down_plan
+        a = gp.a_planes(x, zero, nw, EPS)
+        if with_parts and collecting[0]:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            gp.gemm(a, r7.gate_bw)
+            e1.record()
+            part_events.append((e0, e1))
+        else:
+            gp.gemm(a, r7.gate_bw)
+        d = dp(prepared_w=r7.down_bw)
+        ops.add(gp.residual_out, d, out=r7.out)
+
+    collecting = [False]
+    arms = {"rank7": r7_step, "dense_tcgen05": lambda: dn(x), "dense_cublas": lambda: cb(x)}
+    for fn in arms.values():
+        for _ in range(warmup):
+            fn()
+    torch.cuda.synchronize()
+    collecting[0] = True
+    launches0 = ops.launch_count()
+    times = {k: [] for k in arms}
+    for _ in range(steps):
+        for name, fn in arms.items():
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            times[name].append(e0.elapsed_time(e1))
+    torch.cuda.synchronize()
+    ops.check_status()
+    res = {k: {"mean_ms": statistics.mean(v), "median_ms": statistics.median(v)} for k, v in times.items()}
+    res["launches"] = ops.launch_count() - launches0
+    if with_parts:
+        res["gate_up_ms"] = statistics.mean(e0.elapsed_time(e1) for e0, e1 in part_events)
+    res["objects"] = (r7, x)
+    return res
+
+
+def run_ours(args, rank, world, device):
+    import torch.distributed as dist
+    from lcgemm import ops
+
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.int8, device=device)
+    peak_burst, peak_sustained, peak_kind = measured_peaks()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    if world == 1:
+        cfg = SINGLE
+        with ClockWatch(torch.cuda.current_device()) as cw:
+            head = bench_layer_arms(cfg["tokens"], cfg["hidden"], cfg["inter"], args.steps, args.warmup,
+                                    flush, device, with_parts=True)
+        clocks = cw.summary()
+        r7, x = head.pop("objects")
+        ms = head["rank7"]["mean_ms"]
+        flops = layer_flops(**cfg)
+        value = flops / (ms * 1e-3) / 1e12
+
+        # end to end through the public layer call: input from pinned host memory, result back
+        x_host = x.cpu().pin_memory()
+        out_host = torch.empty_like(x_host).pin_memory()
+        x_dev = torch.empty_like(x)
+
+        def e2e_step():
+            x_dev.copy_(x_host, non_blocking=True)
+            out_host.copy_(r7(x_dev), non_blocking=True)
+
+        e2e_times = timed_steps(e2e_step, args.steps, args.warmup, flush, sync_all)
+        e2e_ms = statistics.mean(e2e_times)
+        ops.check_status()
+
+        by_tokens = {}
+        for tokens in (2048, 8192):
+            del r7, x
+            torch.cuda.empty_cache()
+            sub = bench_layer_arms(tokens, cfg["hidden"], cfg["inter"], max(5, args.steps // 2),
+                                   args.warmup, flush, device)
+            r7, x = sub.pop("objects")
+            by_tokens[str(tokens)] = _arm_summary(sub, layer_flops(tokens, cfg["hidden"], cfg["inter"]))
+        by_tokens[str(cfg["tokens"])] = _arm_summary(head, flops)
+        del r7, x
+        torch.cuda.empty_cache()
+
+        gate_flops = 2.0 * cfg["tokens"] * cfg["hidden"] * 2 * cfg["inter"]
+        gate_ms = head["gate_up_ms"]
+        executed = 0.875 * gate_flops / (gate_ms * 1e-3) / 1e12
+        roofline = {
+            "bound": "tensor", "kernel": "k_gemm<2,true> (chained rank-7 gate_up, 4096x5120x34816)",
+            "achieved": executed, "peak": peak_burst, "unit": "TFLOP/s", "frac": executed / peak_burst,
+            "peak_kind": f"{peak_kind} cuBLAS bf16 burst; sustained {peak_sustained}",
+            "flops_per_launch": 0.875 * gate_flops, "effective_tflops": gate_flops / (gate_ms * 1e-3) / 1e12,
+            "ms_per_launch": gate_ms, "traffic": GATE_UP_DRAM_TRAFFIC_BYTES,
+        }
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": _workload_name(1), **cfg, "l2": "flushed between steps (256 MiB memset)",
+                       "schemes": {"gate_up": "2x2_postsum_cse", "down": "2x2_locality_ordered"}},
+            "clocks": clocks,
+            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
+            "gpu_launches": head["launches"],
+            "speedup_vs_dense_tcgen05_pct": by_tokens[str(cfg["tokens"])]["speedup_vs_dense_tcgen05_pct"],
+            "speedup_vs_cublas_pct": by_tokens[str(cfg["tokens"])]["speedup_vs_cublas_pct"],
+            "by_tokens": by_tokens, "roofline": roofline,
+            "cpu_baseline": cpu_baseline(cfg["hidden"], cfg["inter"]),
+        }
+        print(json.dumps(line))
+        return
+
+    # ------------------------------------------------------------- tensor parallel
+    from lcgemm.tp import TensorParallelMlp
+
+    cfg = TP
+    il = cfg["inter"] // world
+    x, nw, wgu, wd = make_layer_tensors(cfg["tokens"], cfg["hidden"], cfg["inter"], device,
+                                        inter_local=il, rank=rank)
+    layer = TensorParallelMlp(cfg["tokens"], nw, wgu, wd, EPS)
+    launches0 = ops.launch_count()
+    with ClockWatch(torch.cuda.current_device()) as cw:
+        times = timed_steps(lambda: layer(x), args.steps, args.warmup, flush, sync_all,
+                            pre_step=(lambda: dist.barrier()))
+    launches = ops.launch_count() - launches0
+    ops.check_status()
+    x_host = x.cpu().pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+    x_dev = torch.empty_like(x)
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        out = layer(x_dev)
+        if rank == 0:
+            out_host.copy_(out, non_blocking=True)
+
+    e2e_times = timed_steps(e2e_step, args.steps, args.warmup, flush, sync_all,
+                            pre_step=(lambda: dist.barrier()))
+    t = torch.tensor([statistics.mean(times), statistics.mean(e2e_times)], device=device,
+                     dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
+    if rank == 0:
+        flops = layer_flops(**cfg)
+        per_rank_gate = 0.875 * 2.0 * cfg["tokens"] * cfg["hidden"] * 2 * il
+        print(json.dumps({
+            "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": _workload_name(world), **cfg, "parallelism": f"tp{world}",
+                       "all_reduce_bytes": cfg["tokens"] * cfg["hidden"] * 2,
+                       "l2": "flushed between steps (256 MiB memset)"},
+            "clocks": cw.summary(),
+            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": world * x_host.numel() * 2,
+                    "d2h_bytes_per_step": out_host.numel() * 2},
+            "gpu_launches": launches * world,
+            "roofline": {"bound": "tensor", "kernel": "whole step (per-rank rank-7 chain + all-reduce)",
+                         "achieved": 0.875 * flops / (ms * 1e-3) / 1e12 / world, "peak": peak_burst,
+                         "unit": "TFLOP/s per GPU", "frac": 0.875 * flops / (ms * 1e-3) / 1e12 / world / peak_burst,
+                         "peak_kind": f"{peak_kind} cuBLAS bf16 burst", "flops_per_launch": per_rank_gate,
+                         "traffic": None},
+        }))
+
+
+def _arm_summary(res, flops):
+    r7, dt, cb = (res[k]["mean_ms"] for k in ("rank7", "dense_tcgen05", "dense_cublas"))
+    return {"rank7_ms": r7, "dense_tcgen05_ms": dt, "dense_cublas_ms": cb,
+            "rank7_effective_tflops": flops / (r7 * 1e-3) / 1e12,
+            "rank7_executed_tflops": 0.875 * flops / (r7 * 1e-3) / 1e12,
+            "dense_tcgen05_tflops": flops / (dt * 1e-3) / 1e12,
+            "dense_cublas_tflops": flops / (cb * 1e-3) / 1e12,
+            "speedup_vs_dense_tcgen05_pct": (dt / r7 - 1.0) * 100.0,
+            "speedup_vs_cublas_pct": (cb / r7 - 1.0) * 100.0}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch under torchrun); got {world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the rank-7 path has no CPU implementation")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        run_ours(args, rank, world, device)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
