@@ -164,6 +164,33 @@ int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_sche
                       void* preclear, int64_t preclear_bytes, int cta_group,
                       int32_t* status, void* stream);
 
+/* Rank-7 C = A @ B^T straight from the activation matrix, for callers that cannot
+ * allocate device memory.  This entry point has no counterpart in the reference.
+ *
+ * Who needs it: hosts that give all free device memory to their own pool at start-up
+ * (an inference server sizing its KV cache from what is left), so that a plugin's
+ * later cudaMalloc fails or eats into that budget, and serving paths on which
+ * allocation is forbidden because cudaMalloc synchronises the device.
+ *
+ * The A planes -- the scratch lcg_a_planes + lcg_gemm_r7 keep in a caller-owned buffer
+ * -- live in a fixed array of lcg_static_scratch_bytes() (32 MiB) of device memory
+ * inside the library; every GPU that loads the library holds it until the process
+ * exits.  The call allocates and frees nothing.  Limits and rules:
+ *   - rank * ceil(M/2) * round_up(ceil(K/2), 64) * 2 bytes must fit in the array
+ *     (e.g. M = 2048, K = 4096); larger shapes return LCG_ERR_UNSUPPORTED_SHAPE;
+ *   - the first call on a device resolves the array's address (once per device, with
+ *     that device current); make that first call before any stream capture begins;
+ *   - all calls on a device share the one array: calls that overlap on the GPU
+ *     (different streams) race.  Nothing needs clearing between calls -- each call
+ *     rewrites every plane element it reads, padding included;
+ *   - as for lcg_gemm_r7: a (M, K) with lda, B planes from lcg_prepare_b, ldc a
+ *     multiple of 8, and C zeroed by the caller for LCG_SCHEDULE_RANK_SPLIT. */
+int lcg_gemm_r7_static(const lcg_scheme_t* scheme, const void* a, int64_t lda,
+                       const void* b_planes, int64_t ld_b, void* c, int64_t ldc,
+                       int64_t M, int64_t N, int64_t K, int schedule, int cta_group,
+                       int32_t* status, void* stream);
+int64_t lcg_static_scratch_bytes(void);
+
 /* ---- dense-arm seams (the stock layer the rank-7 path is compared with) -- */
 
 /* h = bf16(delta + residual) -> residual_out; x = bf16(rmsnorm(h) * (w + 1))

@@ -16,7 +16,7 @@ CSRC = _PKG.parent / "csrc"
 INCLUDE = _PKG.parent.parent / "include"
 LIB_DIR = _PKG / "_lib"
 LIB_PATH = LIB_DIR / "liblcgemm_b200.so"
-SOURCES = ("lcg_scheme.cu", "lcg_simt.cu", "lcg_gemm.cu")
+SOURCES = ("lcg_scheme.cu", "lcg_simt.cu", "lcg_gemm.cu", "lcg_static.cu")
 
 OK = 0
 ERR_BAD_ARG, ERR_UNSUPPORTED_SHAPE, ERR_MISALIGNED, ERR_SCHEME, ERR_CUDA, ERR_DEVICE_TIMEOUT = (
@@ -44,6 +44,9 @@ SIGNATURES = {
                            _vp, _vp]),
     "lcg_gate_up_chain": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
                                  _vp, _i64, _vp, _i64, _i32, _vp, _vp]),
+    "lcg_gemm_r7_static": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _i32,
+                                  _vp, _vp]),
+    "lcg_static_scratch_bytes": (_i64, []),
     "lcg_add_rmsnorm": (_i32, [_vp, _vp, _vp, _i64, _i64, _f32, _vp, _vp, _vp]),
     "lcg_swiglu": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "lcg_add": (_i32, [_vp, _vp, _vp, _i64, _vp]),
