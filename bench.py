@@ -431,8 +431,114 @@ def _arm_summary(res, flops):
             "speedup_vs_cublas_pct": (cb / r7 - 1.0) * 100.0}
 
 
+# ------------------------------------------------- kernel-level cases and the shape sweep
+SWEEP_KN = ((5120, 34816), (17408, 5120), (6144, 32768), (16384, 6144), (5000, 13999))
+
+
+def _event_times(fn, steps, warmup, flush):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        out.append(e0.elapsed_time(e1))
+    return out
+
+
+def run_case(args, device):
+    """One kernel of the layer on its own (few launches: the form used for ncu captures)."""
+    from lcgemm import ops, scheme as S
+    from lcgemm.seams import build_chain
+
+    m, h, i = args.tokens, SINGLE["hidden"], SINGLE["inter"]
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.int8, device=device)
+    x, nw, wgu, wd = make_layer_tensors(m, h, i, device)
+    gate, down = build_chain((m, h, 2 * i), (m, i, h))
+    zero = torch.zeros_like(x)
+    if args.case in ("gate_up", "norm_planes", "down"):
+        gate_bw = gate.prepare_weight(wgu)
+        a = gate.a_planes(x, zero, nw, EPS)
+        gate.gemm(a, gate_bw)
+        if args.case == "gate_up":
+            fn, flops = (lambda: gate.gemm(a, gate_bw)), 2.0 * m * h * 2 * i
+        elif args.case == "norm_planes":
+            fn, flops = (lambda: gate.a_planes(x, zero, nw, EPS)), 0.0
+        else:
+            down_bw = down.prepare_weight(wd)
+            fn, flops = (lambda: down(prepared_w=down_bw)), 2.0 * m * i * h
+    elif args.case == "dense_gate_up":
+        out = torch.empty((m, 2 * i), device=device, dtype=torch.bfloat16)
+        fn, flops = (lambda: ops.gemm_dense(x, wgu, out=out)), 2.0 * m * h * 2 * i
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    times = _event_times(fn, args.steps, args.warmup, flush)
+    ops.check_status()
+    ms = statistics.mean(times)
+    print(json.dumps({"case": args.case, "tokens": m, "hidden": h, "inter": i, "ms": ms,
+                      "effective_tflops": flops / (ms * 1e-3) / 1e12 if flops else None,
+                      "steps": args.steps, "warmup": args.warmup}))
+
+
+def run_sweep(args, device):
+    """BASELINE config 5: bare rank-7 GEMM (A planes + GEMM, B planes prepared offline) against
+    the dense tcgen05 GEMM and cuBLAS, odd shapes included, one JSON line per shape."""
+    from lcgemm import ops, scheme as S
+    from lcgemm.seams.down import wants_rank_split
+
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.int8, device=device)
+    for m in (2048, 4096, 8192):
+        for k, n in SWEEP_KN:
+            split = wants_rank_split((m, k, n))
+            sch = S.load("2x2_locality_ordered" if split else "2x2_postsum_cse")
+            g = torch.Generator(device=device).manual_seed(m + k + n)
+            a = torch.randn((m, k), generator=g, device=device).to(torch.bfloat16)
+            w = (torch.randn((n, k), generator=g, device=device) * 0.02).to(torch.bfloat16)
+            bp = ops.prepare_b(w, sch)
+            ws = torch.empty(ops.a_plane_shape(sch, m, k), device=device, dtype=torch.bfloat16)
+            ld = (n + 7) // 8 * 8
+            out = torch.empty((m, ld), device=device, dtype=torch.bfloat16)[:, :n]
+            cb_out = torch.empty((m, n), device=device, dtype=torch.bfloat16)
+            arms = {
+                "rank7": lambda: ops.gemm_r7(a, bp, n, sch, out=out, a_workspace=ws, schedule=int(split)),
+                "dense_tcgen05": lambda: ops.gemm_dense(a, w, out=out),
+                "dense_cublas": lambda: torch.matmul(a, w.t(), out=cb_out),
+            }
+            for fn in arms.values():
+                for _ in range(args.warmup):
+                    fn()
+            torch.cuda.synchronize()
+            times = {name: [] for name in arms}
+            for _ in range(args.steps):
+                for name, fn in arms.items():
+                    times[name] += _event_times(fn, 1, 0, flush)
+            ops.check_status()
+            r7, dn, cb = (statistics.mean(times[x]) for x in ("rank7", "dense_tcgen05", "dense_cublas"))
+            fl = 2.0 * m * n * k
+            print(json.dumps({
+                "sweep": "bare_gemm", "M": m, "K": k, "N": n,
+                "schedule": "rank_split" if split else "all_ranks", "scheme": sch.name,
+                "rank7_ms": r7, "dense_tcgen05_ms": dn, "dense_cublas_ms": cb,
+                "rank7_effective_tflops": fl / r7 / 1e9, "rank7_executed_tflops": 0.875 * fl / r7 / 1e9,
+                "dense_tcgen05_tflops": fl / dn / 1e9, "dense_cublas_tflops": fl / cb / 1e9,
+                "speedup_vs_dense_tcgen05_pct": (dn / r7 - 1) * 100, "speedup_vs_cublas_pct": (cb / r7 - 1) * 100,
+                "note": "rank7 time includes forming the A planes; L2 flushed between timed launches"}),
+                flush=True)
+            del a, w, bp, ws, out, cb_out
+            torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default=None,
+                    help="time one kernel alone: gate_up | down | norm_planes | dense_gate_up")
+    ap.add_argument("--tokens", type=int, default=4096, help="token count for --case")
+    ap.add_argument("--sweep", action="store_true", help="bare-GEMM shape sweep (BASELINE config 5)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
@@ -452,6 +558,10 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the rank-7 path has no CPU implementation")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    if args.case or args.sweep:
+        if world != 1:
+            raise SystemExit("--case / --sweep run on one GPU")
+        return run_case(args, device) if args.case else run_sweep(args, device)
     if world > 1:
         import torch.distributed as dist
 

@@ -60,6 +60,13 @@ extern "C" {
                                        contribution is a reduce-add into a C that
                                        arrives zeroed (lcgemm/kernels/down_rank_split.py:106-113,209-216) */
 
+#define LCG_SCHEDULE_HYBRID      2  /* whole waves of tiles walk all products; the tiles of
+                                       the last partial wave are split by product over all
+                                       CTA groups (their C blocks are cleared by a small
+                                       kernel first, then receive reduce-adds only).  Takes
+                                       the place of the reference's two-region tail
+                                       re-tiling (lcgemm/kernels/hetero.py:37-44) */
+
 /* MMA pairing: 1 = one CTA per 128x256 tile, 2 = a 2-CTA pair per 256x256 tile
  * (the reference's tcgen05 CtaGroup.TWO, lcgemm/kernels/sm100.py:186-191). */
 #define LCG_CTA_GROUP_DEFAULT 0
@@ -156,12 +163,15 @@ int lcg_gemm_r7(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,
  * L_r(S) in the interleaved gauge into down_planes (plane_rank * M/2, I/2);
  * optionally zeroes `preclear` (preclear_bytes, multiple of 16) for a
  * rank-split consumer (lcgemm/kernels/sm100.py:779-815).
- * Needs M % 2 == 0, I % 256 == 0, K % 128 == 0. */
+ * `schedule` is LCG_SCHEDULE_ALL_RANKS or LCG_SCHEDULE_HYBRID; with the hybrid schedule the
+ * tail tiles' seven products come from different CTAs and the one that lands last runs the
+ * tile's SwiGLU/plane phase (completion counters live in the library and are left clean).
+ * Needs M % 2 == 0, N % 256 == 0, K % 128 == 0. */
 int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_scheme,
                       const void* a_planes, int64_t ld_a, const void* b_planes, int64_t ld_b,
                       void* z, int64_t ldz, int64_t M, int64_t N, int64_t K,
                       void* down_planes, int64_t ld_planes,
-                      void* preclear, int64_t preclear_bytes, int cta_group,
+                      void* preclear, int64_t preclear_bytes, int schedule, int cta_group,
                       int32_t* status, void* stream);
 
 /* Rank-7 C = A @ B^T straight from the activation matrix, for callers that cannot
@@ -209,6 +219,11 @@ int lcg_swiglu(const void* z, int64_t M, int64_t I, int64_t ldz, void* s, int64_
 int lcg_add(const void* a, const void* b, void* out, int64_t n, void* stream);
 
 /* ---- introspection ------------------------------------------------------- */
+
+/* Clear the library's tail-tile completion counters on the current device.  Only needed
+ * after a launch reported a device-side timeout in its status word (the counters of that
+ * launch may be left mid-count); asynchronous on `stream`. */
+int lcg_reset_state(void* stream);
 
 /* Kernel launches issued by this library in this process (for the bench's
  * `gpu_launches`). */

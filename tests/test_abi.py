@@ -77,7 +77,7 @@ def test_describe_and_argument_checks_do_not_need_a_gpu(native_lib):
     sch = nat.NativeScheme.of(S.load("2x2_postsum_cse")).handle
     fake = ctypes.c_void_p(4096)
     assert native_lib.lcg_gate_up_chain(sch, sch, fake, 64, fake, 64, fake, 300, 64, 300, 128, fake,
-                                        80, None, 0, 0, None, None) == nat.ERR_UNSUPPORTED_SHAPE
+                                        80, None, 0, 0, 0, None, None) == nat.ERR_UNSUPPORTED_SHAPE
     assert native_lib.lcg_norm_planes(sch, fake, fake, fake, 7, 64, 1e-6, fake, fake, 64,
                                       None) == nat.ERR_UNSUPPORTED_SHAPE
     assert native_lib.lcg_gemm_r7(sch, fake, 64, fake, 64, fake, 64, 64, 64, 128, 5, 0, None,

@@ -41,30 +41,45 @@ def test_chain_against_oracle(lc, dims):
     want_out, want_h, want_z, want_pl = O.mlp_chain(
         delta.cpu(), residual.cpu(), nw.cpu(), wgu.cpu(), wd.cpu(), 1e-6, O.Tables(GATE), O.Tables(DOWN))
     assert torch.equal(gate.residual_out.cpu().view(torch.int16), want_h.view(torch.int16))
-    assert rel_fro(z, want_z) <= 2e-3
+    assert rel_fro(z, want_z) <= 8e-3              # hybrid schedule: split tail, unordered bf16 adds
     # planes from the device's own Z must match the oracle's transform of that same Z
     pl_from_dev_z = O.chain_a_planes(z.cpu(), O.Tables(DOWN))
     assert within_ulps(gate.planes, pl_from_dev_z, 1.0, floor=1e-3)
     assert mismatch_fraction(gate.planes, pl_from_dev_z) < 1e-3
-    assert rel_fro(out, want_out) <= 8e-3          # rank-split down: unordered bf16 adds
+    # down from the device's own planes, against the oracle's rank-split model of it
+    prods = O.products(gate.planes.cpu(), O.prepare_down_b(wd.cpu(), O.Tables(DOWN)), 7)
+    assert rel_fro(out, O.combine_as_kernel(prods, O.Tables(DOWN), m, h, rank_split=True)) <= 8e-3
+    assert rel_fro(out, want_out) <= 2e-2           # whole chain, both stages' tolerances stacked
     ref, _ = O.mlp_reference(delta.cpu(), residual.cpu(), nw.cpu(), wgu.cpu(), wd.cpu(), 1e-6)
     assert rel_fro(out, ref) <= 2e-2
 
 
 @pytest.mark.parametrize("group", [1, 2])
-def test_fused_epilogue_equals_unfused_kernels(lc, group):
-    m, h, i = 1024, 512, 1280
+@pytest.mark.parametrize("dims", [(1024, 512, 1280), (2048, 256, 5120)])
+def test_fused_epilogue_equals_unfused_kernels(lc, group, dims):
+    m, h, i = dims
     gs, ds = lc.load(GATE), lc.load(DOWN)
     x, w = seeded((m, h), 1), seeded((2 * i, h), 2, 0.02)
     ap, bp = lc.planes.a_planes(x, gs), lc.planes.prepare_b(w, gs)
     z = torch.empty((m, 2 * i), device="cuda", dtype=torch.bfloat16)
     pl = torch.full((7 * m // 2, i // 2), 3.0, device="cuda", dtype=torch.bfloat16)
     pc = torch.ones((m, 520), device="cuda", dtype=torch.bfloat16)
-    lc.ops.gate_up_chain(gs, ds, ap, bp, z, pl, preclear=pc, cta_group=group)
+    lc.ops.gate_up_chain(gs, ds, ap, bp, z, pl, preclear=pc, schedule=0, cta_group=group)
     z_plain = lc.ops.gemm_r7_planes(gs, ap, bp, m, 2 * i, h, cta_group=group)
-    assert torch.equal(z, z_plain)
+    assert torch.equal(z, z_plain)                          # all-ranks schedule: deterministic
     assert torch.equal(pl, lc.gauge.chain_a_planes(z, ds))
     assert bool((pc == 0).all())
+    # Hybrid schedule: the tail tiles' products arrive as reduce-adds from several CTAs, so Z
+    # agrees within the rank-split tolerance; the planes must still be exactly the transform
+    # of the Z this launch produced (the last arrival runs the plane phase of a tail tile).
+    for _ in range(2):                                      # twice: counters are left clean
+        z2 = torch.full_like(z, 5.0)
+        pl2 = torch.full_like(pl, 3.0)
+        pc.fill_(1.0)
+        lc.ops.gate_up_chain(gs, ds, ap, bp, z2, pl2, preclear=pc, schedule=2, cta_group=group)
+        assert rel_fro(z2, z_plain) <= 8e-3
+        assert torch.equal(pl2, lc.gauge.chain_a_planes(z2, ds))
+        assert bool((pc == 0).all())
 
 
 def test_full_size_chain_qwen_4096(lc):
@@ -76,7 +91,8 @@ def test_full_size_chain_qwen_4096(lc):
     r7 = lc.layer.Rank7MlpLayer(m, nw, wgu, wd)
     out = r7(x).clone()
     gate, down = r7.gate_plan, r7.down_plan
-    assert "544 units" in gate.describe() and "560 units" in down.describe()
+    assert "rank7/hybrid" in gate.describe() and "700 units" in gate.describe()
+    assert "560 units" in down.describe()
     # fused planes == unfused kernel on the same Z, bit for bit
     assert torch.equal(gate.planes, lc.gauge.chain_a_planes(gate.c, gate.plane_scheme))
     # the three arms agree within the stated tolerance

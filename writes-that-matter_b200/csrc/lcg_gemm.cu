@@ -19,6 +19,7 @@
 // the status word and the kernel finishes without blocking again.
 #include <cuda_bf16.h>
 
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -62,6 +63,13 @@ struct CMaps {
   CUtensorMap m[4];
 };
 
+// Completion counters of the tail tiles of a chained hybrid launch: one per (tail tile, CTA of
+// the pair).  A launch takes one slot of the pool in turn; the CTA that records the last of a
+// tile's seven products resets the counter, so a slot is clean again when its launch ends.
+constexpr int kSchedSlots = 64;
+constexpr int kSchedSlotInts = 256;
+__device__ int g_tail_counters[kSchedSlots][kSchedSlotInts];
+
 struct ChainParams {
   const __nv_bfloat16* z;     // the GEMM's own output, re-read L2-hot
   int64_t ldz;
@@ -70,16 +78,21 @@ struct ChainParams {
   int32_t m2;                 // rows per block row
   int32_t inter;              // I: S columns; gate block = z[:, :I], up block = z[:, I:]
   int32_t plane_rank;
-  int32_t iters_max;          // most tiles any CTA group walks
+  int32_t iters_max;          // most work units any CTA group walks
+  int32_t sched_slot;         // which row of g_tail_counters this launch uses
+  int32_t plane_steps_total;  // products per tile (arrivals that complete a tail tile)
   TermTable plane_terms;
   uint4* preclear;            // consumer output to zero, or null
   int64_t preclear_vecs;
 };
 
 struct GemmParams {
-  StepDesc steps[kMaxRank];
-  int32_t steps_per_unit;     // 7 (all products per tile) or 1 (dense, rank split)
-  int32_t rank_split;         // unit = product * tiles + tile
+  StepDesc steps[kMaxRank];        // whole-tile walk: chain plan, store-first scatter (or the dense step)
+  StepDesc steps_split[kMaxRank];  // one product alone, reduce-add only
+  int32_t steps_per_unit;     // steps of a whole-tile unit: 7, or 1 (dense)
+  int32_t rank_split;         // every unit is one product: unit = product * tiles + tile
+  int32_t main_tiles;         // tiles walked whole; the remaining tail_tiles are split by product
+  int32_t tail_tiles;         //   (hybrid schedule; 0 otherwise): unit = main + product * tail + n
   int32_t tiles_m, tiles_n, group_m;
   int32_t num_units;
   int32_t k_blocks;
@@ -93,23 +106,43 @@ struct GemmParams {
 // time span a near-square patch and share operand panels in L2
 // (lcgemm/kernels/sm100.py:78-96,754-772).
 struct UnitCoord {
-  int step0, tm, tn;
+  int step0, nsteps;   // steps [step0, step0 + nsteps) of the table `split` selects
+  int split;           // 1: steps_split (single product, reduce-add), 0: steps
+  int tile;            // linear tile index
+  int tail;            // index among the tail tiles, or -1
+  int tm, tn;
 };
-__device__ __forceinline__ UnitCoord decode_unit(const GemmParams& p, int u) {
-  const int tiles = p.tiles_m * p.tiles_n;
-  UnitCoord c;
-  int t = u;
-  c.step0 = 0;
-  if (p.rank_split) {
-    c.step0 = u / tiles;
-    t = u - c.step0 * tiles;
-  }
+__device__ __forceinline__ void tile_coord(const GemmParams& p, int t, int& tm, int& tn) {
   const int band_sz = p.group_m * p.tiles_n;
   const int band = t / band_sz;
   const int rem = t - band * band_sz;
   const int gm = min(p.group_m, p.tiles_m - band * p.group_m);
-  c.tm = band * p.group_m + rem % gm;
-  c.tn = rem / gm;
+  tm = band * p.group_m + rem % gm;
+  tn = rem / gm;
+}
+__device__ __forceinline__ UnitCoord decode_unit(const GemmParams& p, int u) {
+  UnitCoord c;
+  c.tail = -1;
+  if (p.rank_split) {
+    const int tiles = p.tiles_m * p.tiles_n;
+    c.step0 = u / tiles;
+    c.tile = u - c.step0 * tiles;
+    c.nsteps = 1;
+    c.split = 1;
+  } else if (u < p.main_tiles) {
+    c.step0 = 0;
+    c.nsteps = p.steps_per_unit;
+    c.split = 0;
+    c.tile = u;
+  } else {
+    const int v = u - p.main_tiles;
+    c.step0 = v / p.tail_tiles;
+    c.tail = v - c.step0 * p.tail_tiles;
+    c.tile = p.main_tiles + c.tail;
+    c.nsteps = 1;
+    c.split = 1;
+  }
+  tile_coord(p, c.tile, c.tm, c.tn);
   return c;
 }
 
@@ -160,8 +193,11 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
   const uint32_t misc = bar_base + 8u * (2 * T::kStages + 4);
   volatile uint32_t* misc_gen =
       reinterpret_cast<volatile uint32_t*>(smem_gen + (misc - base));
-  // misc_gen[0] = TMEM base, [1] = abort flag, [2] = finished-tile counter
+  // misc_gen[0] = TMEM base, [1] = abort flag, [2] = units the epilogue has finished,
+  // [3] = units the plane warps have finished, [4..19] = ring of plane jobs (tile index or -1)
   const uint32_t z_done_addr = misc + 8;
+  const uint32_t plane_done_addr = misc + 12;
+  constexpr int kJobRing = 16;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -182,6 +218,7 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
     }
     misc_gen[1] = 0u;
     misc_gen[2] = 0u;
+    misc_gen[3] = 0u;
     fence_mbar_init();
     prefetch_tensormap(&tma_a);
     prefetch_tensormap(&tma_b);
@@ -206,10 +243,11 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
       uint32_t it = 0;
       for (int u = group_id; u < p.num_units; u += num_groups) {
         const UnitCoord uc = decode_unit(p, u);
-        for (int s = uc.step0; s < uc.step0 + p.steps_per_unit; ++s) {
-          const int a_row = p.steps[s].a_plane * p.a_plane_rows + uc.tm * T::kTileM +
+        for (int s = uc.step0; s < uc.step0 + uc.nsteps; ++s) {
+          const StepDesc& sd = uc.split ? p.steps_split[s] : p.steps[s];
+          const int a_row = sd.a_plane * p.a_plane_rows + uc.tm * T::kTileM +
                             static_cast<int>(cta_rank) * kBM;
-          const int b_row = p.steps[s].b_plane * p.b_plane_rows + uc.tn * kBN +
+          const int b_row = sd.b_plane * p.b_plane_rows + uc.tn * kBN +
                             static_cast<int>(cta_rank) * T::kBRows;
           for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
             const uint32_t stage = it % T::kStages;
@@ -238,13 +276,13 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
       uint32_t it = 0, acc_it = 0;
       for (int u = group_id; u < p.num_units; u += num_groups) {
         const UnitCoord uc = decode_unit(p, u);
-        for (int s = uc.step0; s < uc.step0 + p.steps_per_unit; ++s, ++acc_it) {
+        for (int s = uc.step0; s < uc.step0 + uc.nsteps; ++s, ++acc_it) {
           const uint32_t as = acc_it & 1u;
           const uint32_t aphase = (acc_it >> 1) & 1u;
           mbar_wait(acc_empty_bar(as), aphase ^ 1u, ctl, kCodeMmaAcc);
           tcgen05_fence_after();
           const uint32_t d_tmem = tmem_base + as * kBN;
-          const uint32_t keep = p.steps[s].clear ? 0u : 1u;
+          const uint32_t keep = (uc.split || p.steps[s].clear) ? 0u : 1u;
           for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
             const uint32_t stage = it % T::kStages;
             const uint32_t phase = (it / T::kStages) & 1u;
@@ -272,17 +310,17 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
     const bool issuer = warp == kEpiWarp0 && lane == 0;
     const uint32_t acc_empty_remote =
         kCtaGroup == 2 ? mapa_shared(acc_empty_bar(0), 0) : acc_empty_bar(0);
-    uint32_t acc_it = 0, epi_it = 0, tiles_done = 0;
+    uint32_t acc_it = 0, epi_it = 0, units_done = 0;
     for (int u = group_id; u < p.num_units; u += num_groups) {
       const UnitCoord uc = decode_unit(p, u);
       const int row0 = uc.tm * T::kTileM + static_cast<int>(cta_rank) * kBM;
       const int col0 = uc.tn * kBN;
-      for (int s = uc.step0; s < uc.step0 + p.steps_per_unit; ++s, ++acc_it) {
+      for (int s = uc.step0; s < uc.step0 + uc.nsteps; ++s, ++acc_it) {
         const uint32_t as = acc_it & 1u;
         const uint32_t aphase = (acc_it >> 1) & 1u;
         mbar_wait(acc_full_bar(as), aphase, ctl, kCodeEpilogue);
         tcgen05_fence_after();
-        const StepDesc& sd = p.steps[s];
+        const StepDesc& sd = uc.split ? p.steps_split[s] : p.steps[s];
         for (int g = 0; g < sd.ngroups; ++g) {
           const float coeff = static_cast<float>(sd.group[g].coeff);
 #pragma unroll 1
@@ -338,12 +376,30 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
         }
       }
       if constexpr (kChain) {
-        // The tile's C blocks are final once every bulk copy has landed; publish
-        // that to the plane warps (single writer per tile, so ordering is CTA-local).
+        // Hand the unit to the plane warps.  A whole tile's C blocks are final once this CTA's
+        // bulk copies have landed (single writer).  A tail tile is final when the last of its
+        // seven products has landed, whichever CTA that is: each records its arrival in the
+        // tile's counter and the one that completes the count takes the plane job.
         if (issuer) {
           bulk_wait_group<0>();
           fence_proxy_async_all();
-          st_release_shared(z_done_addr, ++tiles_done);
+          int job = uc.tile;
+          if (uc.tail >= 0) {
+            int* cnt = &g_tail_counters[p.chain.sched_slot][uc.tail * 2 + static_cast<int>(cta_rank)];
+            __threadfence();
+            const int seen = atomicAdd(cnt, 1);
+            if (seen == p.chain.plane_steps_total - 1) {
+              __threadfence();
+              *cnt = 0;
+            } else {
+              job = -1;
+            }
+          }
+          // the ring entry being overwritten must have been consumed
+          if (units_done >= kJobRing - 1)
+            counter_wait(plane_done_addr, units_done - (kJobRing - 2), ctl, kCodePlane);
+          misc_gen[4 + (units_done % kJobRing)] = static_cast<uint32_t>(job);
+          st_release_shared(z_done_addr, ++units_done);
         }
         __syncwarp();
       }
@@ -352,14 +408,15 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
     __syncwarp();
   } else if constexpr (kChain) {
     // ------------------------------------------------------------- plane warps
-    // 256 threads; 16 slots across (chunk pair, 8-column vector), 16 rows per step.
+    // 256 threads; 16 slots across (chunk pair, 8-column vector), 16 rows per pass, two
+    // passes (16 x 16-byte loads per thread) in flight at a time.
     const ChainParams& ch = p.chain;
     const int ptid = threadIdx.x - kPlaneWarp0 * 32;
     const int slot = ptid & 15;
     const int pair = slot >> 3;
     const int vc = slot & 7;
     const int rsub = ptid >> 4;
-    uint32_t tile_no = 0;
+    const int tiles_total = p.tiles_m * p.tiles_n;
     const int64_t clear_stride =
         static_cast<int64_t>(gridDim.x) * kPlaneThreads * ch.iters_max;
     auto clear_share = [&](int t) {
@@ -369,66 +426,84 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
            i < ch.preclear_vecs; i += clear_stride)
         ch.preclear[i] = zero;
     };
-    for (int u = group_id; u < p.num_units; u += num_groups) {
-      const UnitCoord uc = decode_unit(p, u);
-      clear_share(static_cast<int>(tile_no));
-      ++tile_no;
-      counter_wait(z_done_addr, tile_no, ctl, kCodePlane);
-      fence_proxy_async_all();
-      const int row_base = uc.tm * T::kTileM + static_cast<int>(cta_rank) * kBM;
-      const int scol = uc.tn * kBN + pair * 128 + vc * 8;     // S column of chunk h = 0
-      const int pcol = uc.tn * (kBN / 2) + pair * 64 + vc * 8;
-      if (scol + 64 < ch.inter) {
+    uint32_t seq = 0;
+    for (int u = group_id; u < p.num_units; u += num_groups, ++seq) {
+      clear_share(static_cast<int>(seq));
+      counter_wait(z_done_addr, seq + 1, ctl, kCodePlane);
+      const int job = static_cast<int>(misc_gen[4 + (seq % kJobRing)]);
+      // A job names a tile whose four C blocks are final.  (After a run-out wait the ring may
+      // hold anything: only a valid tile index is ever acted on.)
+      if (job >= 0 && job < tiles_total && misc_gen[1] == 0u) {
+        fence_proxy_async_all();
+        int tm, tn;
+        tile_coord(p, job, tm, tn);
+        const int row_base = tm * T::kTileM + static_cast<int>(cta_rank) * kBM;
+        const int scol = tn * kBN + pair * 128 + vc * 8;     // S column of chunk h = 0
+        const int pcol = tn * (kBN / 2) + pair * 64 + vc * 8;
+        if (scol + 64 < ch.inter) {
 #pragma unroll 1
-        for (int step = 0; step < kBM / 16; ++step) {
-          const int rho = row_base + rsub + step * 16;
-          if (rho >= ch.m2) break;
-          uint4 q[2][2][2];
+          for (int step = 0; step < kBM / 32; ++step) {
+            uint4 q[2][2][2][2];
+            int rho[2];
 #pragma unroll
-          for (int i = 0; i < 2; ++i)
+            for (int t = 0; t < 2; ++t) {
+              rho[t] = row_base + rsub + (2 * step + t) * 16;
+              if (rho[t] < ch.m2) {
 #pragma unroll
-            for (int j = 0; j < 2; ++j)
+                for (int i = 0; i < 2; ++i)
 #pragma unroll
-              for (int hh = 0; hh < 2; ++hh)
-                q[i][j][hh] = __ldcg(reinterpret_cast<const uint4*>(
-                    ch.z + (static_cast<int64_t>(i) * ch.m2 + rho) * ch.ldz +
-                    static_cast<int64_t>(j) * ch.inter + scol + hh * 64));
-          float sv[4][8];
+                  for (int j = 0; j < 2; ++j)
 #pragma unroll
-          for (int i = 0; i < 2; ++i)
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-              float g[8], uu[8];
-              unpack_bf16x8(q[i][0][hh], g);
-              unpack_bf16x8(q[i][1][hh], uu);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) sv[i * 2 + hh][e] = silu_dev(g[e]) * uu[e];
+                    for (int hh = 0; hh < 2; ++hh)
+                      q[t][i][j][hh] = __ldcg(reinterpret_cast<const uint4*>(
+                          ch.z + (static_cast<int64_t>(i) * ch.m2 + rho[t]) * ch.ldz +
+                          static_cast<int64_t>(j) * ch.inter + scol + hh * 64));
+              }
             }
-          for (int r = 0; r < ch.plane_rank; ++r) {
-            float o[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) o[e] = 0.f;
+            for (int t = 0; t < 2; ++t) {
+              if (rho[t] >= ch.m2) continue;
+              float sv[4][8];
 #pragma unroll
-            for (int x = 0; x < 4; ++x) {
-              const int cf = ch.plane_terms.coef[r][x];
-              if (cf == 0) continue;
-              const float w = static_cast<float>(cf);
+              for (int i = 0; i < 2; ++i)
 #pragma unroll
-              for (int e = 0; e < 8; ++e) o[e] = fmaf(w, sv[x][e], o[e]);
+                for (int hh = 0; hh < 2; ++hh) {
+                  float g[8], uu[8];
+                  unpack_bf16x8(q[t][i][0][hh], g);
+                  unpack_bf16x8(q[t][i][1][hh], uu);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) sv[i * 2 + hh][e] = silu_dev(g[e]) * uu[e];
+                }
+              for (int r = 0; r < ch.plane_rank; ++r) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = 0.f;
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                  const int cf = ch.plane_terms.coef[r][x];
+                  if (cf == 0) continue;
+                  const float w = static_cast<float>(cf);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) o[e] = fmaf(w, sv[x][e], o[e]);
+                }
+                uint4 outv;
+                outv.x = pack_bf16x2(o[0], o[1]);
+                outv.y = pack_bf16x2(o[2], o[3]);
+                outv.z = pack_bf16x2(o[4], o[5]);
+                outv.w = pack_bf16x2(o[6], o[7]);
+                *reinterpret_cast<uint4*>(ch.planes +
+                                          (static_cast<int64_t>(r) * ch.m2 + rho[t]) * ch.ld_planes +
+                                          pcol) = outv;
+              }
             }
-            uint4 outv;
-            outv.x = pack_bf16x2(o[0], o[1]);
-            outv.y = pack_bf16x2(o[2], o[3]);
-            outv.z = pack_bf16x2(o[4], o[5]);
-            outv.w = pack_bf16x2(o[6], o[7]);
-            *reinterpret_cast<uint4*>(ch.planes +
-                                      (static_cast<int64_t>(r) * ch.m2 + rho) * ch.ld_planes +
-                                      pcol) = outv;
           }
         }
       }
+      // every plane thread has read its ring entry: the epilogue may reuse it
+      named_bar_sync(2, kPlaneThreads);
+      if (ptid == 0) st_release_shared(plane_done_addr, seq + 1);
     }
-    for (int t = static_cast<int>(tile_no); t < ch.iters_max; ++t) clear_share(t);
+    for (int t = static_cast<int>(seq); t < ch.iters_max; ++t) clear_share(t);
   }
 
   // ------------------------------------------------------------------ teardown
@@ -448,6 +523,34 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
   if (warp == 1) {
     tcgen05_fence_after();
     tmem_dealloc<kCtaGroup>(tmem_base, kTmemCols);
+  }
+}
+
+// Zero the C blocks of the tail tiles of a hybrid launch (their products arrive as
+// reduce-adds from several CTAs).  grid = (tail tiles, 4 blocks), 256 threads.
+struct ZeroArgs {
+  __nv_bfloat16* c;
+  int64_t ldc;
+  int32_t m, n, m2, n2, tile_m;
+};
+__global__ void __launch_bounds__(256)
+k_zero_tail_tiles(const __grid_constant__ GemmParams p, const ZeroArgs z) {
+  int tm, tn;
+  tile_coord(p, p.main_tiles + static_cast<int>(blockIdx.x), tm, tn);
+  const int bi = blockIdx.y >> 1, bj = blockIdx.y & 1;
+  const int rows = bi == 0 ? z.m2 : z.m - z.m2;
+  const int cols = bj == 0 ? z.n2 : z.n - z.n2;
+  const int r1 = min(tm * z.tile_m + z.tile_m, rows);
+  const int c1 = min(tn * kBN + kBN, cols);
+  __nv_bfloat16* base = z.c + static_cast<int64_t>(bi) * z.m2 * z.ldc + static_cast<int64_t>(bj) * z.n2;
+  const int col = tn * kBN + (threadIdx.x & 31) * 8;
+  for (int row = tm * z.tile_m + (threadIdx.x >> 5); row < r1; row += 8) {
+    __nv_bfloat16* ptr = base + static_cast<int64_t>(row) * z.ldc + col;
+    if (col + 8 <= c1) {
+      *reinterpret_cast<uint4*>(ptr) = make_uint4(0u, 0u, 0u, 0u);
+    } else {
+      for (int e = 0; col + e < c1; ++e) ptr[e] = __float2bfloat16(0.f);
+    }
   }
 }
 
@@ -595,17 +698,57 @@ int fill_r7(const lcg_scheme* scheme, const void* a_planes, int64_t ld_a, const 
     }
   std::memset(p, 0, sizeof(*p));
   const bool split = schedule == LCG_SCHEDULE_RANK_SPLIT;
-  for (int t = 0; t < scheme->rank; ++t) p->steps[t] = split ? scheme->rank_split[t] : scheme->all_ranks[t];
-  p->steps_per_unit = split ? 1 : scheme->rank;
+  for (int t = 0; t < scheme->rank; ++t) {
+    p->steps[t] = scheme->all_ranks[t];
+    p->steps_split[t] = scheme->rank_split[t];
+  }
+  p->steps_per_unit = scheme->rank;
   p->rank_split = split ? 1 : 0;
   p->tiles_m = static_cast<int>((g.m2 + tile_m - 1) / tile_m);
   p->tiles_n = static_cast<int>((g.n2 + kBN - 1) / kBN);
-  p->group_m = pick_group_m(p->tiles_m, sm_count() / cta_group);
-  p->num_units = p->tiles_m * p->tiles_n * (split ? scheme->rank : 1);
+  const int groups = sm_count() / cta_group;
+  p->group_m = pick_group_m(p->tiles_m, groups);
+  const int tiles = p->tiles_m * p->tiles_n;
+  p->main_tiles = tiles;
+  p->tail_tiles = 0;
+  if (schedule == LCG_SCHEDULE_HYBRID) {
+    // Whole waves walk all products per tile; the last partial wave is split by product when
+    // that shortens it: ceil(rank * tail / groups) single steps against `rank` steps.
+    const int tail = tiles % groups;
+    const int split_steps = (scheme->rank * tail + groups - 1) / groups;
+    if (tail > 0 && split_steps <= scheme->rank - 2 && 2 * tail <= kSchedSlotInts) {
+      p->main_tiles = tiles - tail;
+      p->tail_tiles = tail;
+    }
+  }
+  p->num_units = split ? tiles * scheme->rank : p->main_tiles + scheme->rank * p->tail_tiles;
   p->k_blocks = static_cast<int>(g.k2p / kBK);
   p->a_plane_rows = static_cast<int>(g.m2);
   p->b_plane_rows = static_cast<int>(g.n2);
   return LCG_OK;
+}
+
+// The C blocks of the tail tiles receive reduce-adds only: clear them first, on the stream.
+int zero_tail_tiles(const GemmParams& p, void* c, int64_t ldc, int64_t M, int64_t N,
+                    const R7Geometry& g, int cta_group, cudaStream_t stream) {
+  if (p.tail_tiles == 0) return LCG_OK;
+  ZeroArgs z;
+  z.c = static_cast<__nv_bfloat16*>(c);
+  z.ldc = ldc;
+  z.m = static_cast<int32_t>(M);
+  z.n = static_cast<int32_t>(N);
+  z.m2 = static_cast<int32_t>(g.m2);
+  z.n2 = static_cast<int32_t>(g.n2);
+  z.tile_m = kBM * cta_group;
+  k_zero_tail_tiles<<<dim3(static_cast<unsigned>(p.tail_tiles), 4), 256, 0, stream>>>(p, z);
+  LCG_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return LCG_OK;
+}
+
+int next_sched_slot() {
+  static std::atomic<unsigned> turn{0};
+  return static_cast<int>(turn.fetch_add(1, std::memory_order_relaxed) % kSchedSlots);
 }
 
 }  // namespace
@@ -643,6 +786,7 @@ extern "C" int lcg_gemm_dense(const void* a, int64_t lda, const void* b, int64_t
   p.tiles_n = static_cast<int>((N + kBN - 1) / kBN);
   p.group_m = pick_group_m(p.tiles_m, sm_count() / cta_group);
   p.num_units = p.tiles_m * p.tiles_n;
+  p.main_tiles = p.num_units;
   p.k_blocks = static_cast<int>((K + kBK - 1) / kBK);
   p.status = status;
   auto st_ = static_cast<cudaStream_t>(stream);
@@ -654,7 +798,8 @@ extern "C" int lcg_gemm_r7(const lcg_scheme_t* scheme, const void* a_planes, int
                            int64_t N, int64_t K, int schedule, int cta_group, int32_t* status,
                            void* stream) {
   if (!scheme || !a_planes || !b_planes || !c) return fail(LCG_ERR_BAD_ARG, "NULL operand");
-  if (schedule != LCG_SCHEDULE_ALL_RANKS && schedule != LCG_SCHEDULE_RANK_SPLIT)
+  if (schedule != LCG_SCHEDULE_ALL_RANKS && schedule != LCG_SCHEDULE_RANK_SPLIT &&
+      schedule != LCG_SCHEDULE_HYBRID)
     return fail(LCG_ERR_BAD_ARG, "unknown schedule %d", schedule);
   cta_group = resolve_group(cta_group);
   if (cta_group != 1 && cta_group != 2) return fail(LCG_ERR_BAD_ARG, "cta_group must be 0, 1 or 2");
@@ -670,6 +815,7 @@ extern "C" int lcg_gemm_r7(const lcg_scheme_t* scheme, const void* a_planes, int
     return e;
   p.status = status;
   auto st_ = static_cast<cudaStream_t>(stream);
+  if (int e = zero_tail_tiles(p, c, ldc, M, N, g, cta_group, st_)) return e;
   return cta_group == 1 ? launch<1, false>(ma, mb, mc, p, st_) : launch<2, false>(ma, mb, mc, p, st_);
 }
 
@@ -677,10 +823,13 @@ extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t*
                                  const void* a_planes, int64_t ld_a, const void* b_planes,
                                  int64_t ld_b, void* z, int64_t ldz, int64_t M, int64_t N, int64_t K,
                                  void* down_planes, int64_t ld_planes, void* preclear,
-                                 int64_t preclear_bytes, int cta_group, int32_t* status,
-                                 void* stream) {
+                                 int64_t preclear_bytes, int schedule, int cta_group,
+                                 int32_t* status, void* stream) {
   if (!scheme || !plane_scheme || !a_planes || !b_planes || !z || !down_planes)
     return fail(LCG_ERR_BAD_ARG, "NULL operand");
+  if (schedule != LCG_SCHEDULE_ALL_RANKS && schedule != LCG_SCHEDULE_HYBRID)
+    return fail(LCG_ERR_BAD_ARG, "the chained GEMM runs the all-ranks or the hybrid schedule, got %d",
+                schedule);
   cta_group = resolve_group(cta_group);
   if (cta_group != 1 && cta_group != 2) return fail(LCG_ERR_BAD_ARG, "cta_group must be 0, 1 or 2");
   if (M % 2 != 0 || N % 256 != 0 || K % 128 != 0)
@@ -703,8 +852,8 @@ extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t*
   CUtensorMap ma, mb;
   CMaps mc;
   GemmParams p;
-  if (int e = fill_r7(scheme, a_planes, ld_a, b_planes, ld_b, z, ldz, M, N, g, LCG_SCHEDULE_ALL_RANKS,
-                      cta_group, &ma, &mb, &mc, &p))
+  if (int e = fill_r7(scheme, a_planes, ld_a, b_planes, ld_b, z, ldz, M, N, g, schedule, cta_group,
+                      &ma, &mb, &mc, &p))
     return e;
   p.status = status;
   ChainParams& ch = p.chain;
@@ -715,11 +864,14 @@ extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t*
   ch.m2 = static_cast<int32_t>(g.m2);
   ch.inter = static_cast<int32_t>(inter);
   ch.plane_rank = plane_scheme->rank;
+  ch.plane_steps_total = scheme->rank;
+  ch.sched_slot = next_sched_slot();
   for (int r = 0; r < plane_scheme->rank; ++r)
     for (int x = 0; x < 4; ++x) ch.plane_terms.coef[r][x] = plane_scheme->a[r][x];
   ch.preclear = preclear_bytes > 0 ? static_cast<uint4*>(preclear) : nullptr;
   ch.preclear_vecs = preclear_bytes / 16;
   auto st_ = static_cast<cudaStream_t>(stream);
+  if (int e = zero_tail_tiles(p, z, ldz, M, N, g, cta_group, st_)) return e;
   return cta_group == 1 ? launch<1, true>(ma, mb, mc, p, st_) : launch<2, true>(ma, mb, mc, p, st_);
 }
 
@@ -742,13 +894,27 @@ extern "C" int lcg_describe_gemm(int64_t M, int64_t N, int64_t K, int rank7, int
   }
   const int64_t tm = (rows + tile_m - 1) / tile_m, tn = (cols + kBN - 1) / kBN;
   const int groups = sm_count() / cta_group;
-  const int64_t units = tm * tn * units_mul;
+  int64_t units = tm * tn * units_mul;
+  if (rank7 && schedule == LCG_SCHEDULE_HYBRID) {
+    const int64_t tail = (tm * tn) % groups;
+    if (tail > 0 && (7 * tail + groups - 1) / groups <= 5 && 2 * tail <= kSchedSlotInts)
+      units = tm * tn - tail + 7 * tail;
+  }
   return snprintf(buf, buflen,
                   "%s %lldx%lldx%lld: tile %dx%dx%d cta_group=%d stages=%d smem=%dB tmem=512 cols (2 acc "
                   "stages); %lldx%lld tiles, %lld units over %d CTA groups (%.2f waves), %lld k-blocks/step",
-                  rank7 ? (schedule == LCG_SCHEDULE_RANK_SPLIT ? "rank7/rank-split" : "rank7/all-ranks")
+                  rank7 ? (schedule == LCG_SCHEDULE_RANK_SPLIT ? "rank7/rank-split"
+                           : schedule == LCG_SCHEDULE_HYBRID ? "rank7/hybrid" : "rank7/all-ranks")
                         : "dense",
                   (long long)M, (long long)K, (long long)N, tile_m, kBN, kBK, cta_group, stages, smem,
                   (long long)tm, (long long)tn, (long long)units, groups,
                   static_cast<double>(units) / groups, (long long)((kk + kBK - 1) / kBK));
+}
+
+extern "C" int lcg_reset_state(void* stream) {
+  void* ptr = nullptr;
+  LCG_CUDA_OK(cudaGetSymbolAddress(&ptr, g_tail_counters));
+  LCG_CUDA_OK(cudaMemsetAsync(ptr, 0, sizeof(int) * kSchedSlots * kSchedSlotInts,
+                              static_cast<cudaStream_t>(stream)));
+  return LCG_OK;
 }

@@ -21,7 +21,7 @@ SOURCES = ("lcg_scheme.cu", "lcg_simt.cu", "lcg_gemm.cu", "lcg_static.cu")
 OK = 0
 ERR_BAD_ARG, ERR_UNSUPPORTED_SHAPE, ERR_MISALIGNED, ERR_SCHEME, ERR_CUDA, ERR_DEVICE_TIMEOUT = (
     -1, -2, -3, -4, -5, -6)
-SCHEDULE_ALL_RANKS, SCHEDULE_RANK_SPLIT = 0, 1
+SCHEDULE_ALL_RANKS, SCHEDULE_RANK_SPLIT, SCHEDULE_HYBRID = 0, 1, 2
 
 _c = ctypes
 _vp, _i64, _i32, _f32 = _c.c_void_p, _c.c_int64, _c.c_int, _c.c_float
@@ -43,7 +43,8 @@ SIGNATURES = {
     "lcg_gemm_r7": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _i32,
                            _vp, _vp]),
     "lcg_gate_up_chain": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
-                                 _vp, _i64, _vp, _i64, _i32, _vp, _vp]),
+                                 _vp, _i64, _vp, _i64, _i32, _i32, _vp, _vp]),
+    "lcg_reset_state": (_i32, [_vp]),
     "lcg_gemm_r7_static": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _i32,
                                   _vp, _vp]),
     "lcg_static_scratch_bytes": (_i64, []),

@@ -43,6 +43,7 @@ def check_status(device=None) -> None:
     code = int(word[0].item())
     if code != 0:
         word.zero_()
+        lib().lcg_reset_state(stream_ptr())
         raise RuntimeError(
             f"lcgemm_b200: a device-side wait ran out (code {code}: 101 producer, 102/103 MMA "
             f"issuer, 104 epilogue, 105 plane warps); results of that launch are invalid")
@@ -186,7 +187,7 @@ def gemm_r7(a: torch.Tensor, b_pl: torch.Tensor, n: int, scheme, out: torch.Tens
 
 
 def gate_up_chain(scheme, plane_scheme, a_pl, b_pl, z, down_planes, preclear=None,
-                  cta_group: int = 0) -> None:
+                  schedule: int = nat.SCHEDULE_HYBRID, cta_group: int = 0) -> None:
     for t, what in ((a_pl, "A planes"), (b_pl, "B planes"), (z, "z"), (down_planes, "down planes")):
         _need(t, what)
     m, n = z.shape
@@ -205,7 +206,7 @@ def gate_up_chain(scheme, plane_scheme, a_pl, b_pl, z, down_planes, preclear=Non
     check(lib().lcg_gate_up_chain(NativeScheme.of(scheme).handle, NativeScheme.of(plane_scheme).handle,
                                   ptr(a_pl), a_pl.stride(0), ptr(b_pl), b_pl.stride(0), ptr(z),
                                   z.stride(0), m, n, k, ptr(down_planes), down_planes.stride(0),
-                                  pc_ptr, pc_bytes, cta_group, ptr(status_word(z.device)),
+                                  pc_ptr, pc_bytes, schedule, cta_group, ptr(status_word(z.device)),
                                   stream_ptr()))
 
 

@@ -13,6 +13,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops, planes as lc_planes
+from .._native import SCHEDULE_ALL_RANKS, SCHEDULE_HYBRID
 from ..scheme import Scheme
 
 
@@ -22,7 +23,8 @@ class GateUpPlan:
 
     seam = "gate_up"
 
-    def __init__(self, scheme: Scheme, shape, *, plane_scheme: Scheme, cta_group: int = 0):
+    def __init__(self, scheme: Scheme, shape, *, plane_scheme: Scheme, cta_group: int = 0,
+                 schedule: int = SCHEDULE_HYBRID):
         m, k, n = shape
         if m % 2 or n % 256 or k % 128:
             raise ValueError(
@@ -32,6 +34,9 @@ class GateUpPlan:
         self.shape = tuple(shape)                       # (M, K, N)
         self.plane_scheme = plane_scheme
         self.cta_group = cta_group
+        # Hybrid: whole waves walk all products per tile, the last partial wave is split by
+        # product (the role of the reference's per-shape tail policies, lcgemm/seams/gate_up.py:42-68).
+        self.schedule = schedule
         dev = torch.device("cuda", torch.cuda.current_device())
         bf = torch.bfloat16
         self.a = torch.empty(ops.a_plane_shape(scheme, m, k), device=dev, dtype=bf)
@@ -58,7 +63,7 @@ class GateUpPlan:
         c = self.c if out is None else out
         ops.gate_up_chain(self.scheme, self.plane_scheme, a_planes, prepared_w, c, self.planes,
                           preclear=None if self.preclear is self.c else self.preclear,
-                          cta_group=self.cta_group)
+                          schedule=self.schedule, cta_group=self.cta_group)
         return c
 
     def __call__(self, *pre_inputs, prepared_w, out=None, residual_out=None):
@@ -70,7 +75,7 @@ class GateUpPlan:
             m, k, n = self.shape
             self._desc = (
                 f"FusedNormResidual({self.scheme.name})\n"
-                + ops.describe_gemm(m, n, k, True, 0, self.cta_group)
+                + ops.describe_gemm(m, n, k, True, self.schedule, self.cta_group)
                 + f"; chained planes {self.plane_scheme.name}"
                 + ("; clears the consumer output" if self.preclear is not self.c else ""))
         return self._desc
