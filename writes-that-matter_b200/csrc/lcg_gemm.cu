@@ -170,7 +170,9 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& q, float (&f)[8]) {
   }
 }
 
-__device__ __forceinline__ float silu_dev(float g) { return g / (1.0f + __expf(-g)); }
+// silu(g) = g / (1 + e^-g) with the fast exponential and reciprocal (2 ulp each); large |g| is safe:
+// e^-g -> inf gives -0, e^-g -> 0 gives g.
+__device__ __forceinline__ float silu_dev(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
 template <int kCtaGroup, bool kChain>
 __global__ void __launch_bounds__(kChain ? kThreadsChain : kThreadsPlain, 1)
@@ -429,7 +431,8 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
     uint32_t seq = 0;
     for (int u = group_id; u < p.num_units; u += num_groups, ++seq) {
       clear_share(static_cast<int>(seq));
-      counter_wait(z_done_addr, seq + 1, ctl, kCodePlane);
+      if (lane == 0) counter_wait(z_done_addr, seq + 1, ctl, kCodePlane);   // one poller per warp
+      __syncwarp();
       const int job = static_cast<int>(misc_gen[4 + (seq % kJobRing)]);
       // A job names a tile whose four C blocks are final.  (After a run-out wait the ring may
       // hold anything: only a valid tile index is ever acted on.)

@@ -141,7 +141,7 @@ __device__ __noinline__ void counter_wait(uint32_t addr, uint32_t at_least, cons
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (ld_acquire_shared(addr) < at_least) {
-    __nanosleep(64);
+    __nanosleep(256);
     if ((++spins & 0xffu) == 0) {
       if (*ctl.abort_flag) return;
       if (globaltimer_ns() - t0 > kWaitLimitNs) {

@@ -196,7 +196,7 @@ k_norm_planes(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __re
 }
 
 // --------------------------------------------------------- SwiGLU + planes
-__device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + __expf(-g)); }
+__device__ __forceinline__ float silu_f32(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
 // One thread per (row rho of a block row, 8-column vector of a plane).  Plane
 // column l sits in chunk pair l / 64; its two S columns are 64 apart.
