@@ -49,8 +49,8 @@ EPS = 1e-6
 CPU_SAMPLE_TOKENS = 256
 FLUSH_BYTES = 256 << 20
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate_up launch at the headline shape,
-# from the ncu capture summarised in profiles/; None until a capture exists.
-GATE_UP_DRAM_TRAFFIC_BYTES = None
+# from the ncu capture summarised in profiles/k_gemm_gate_up_chain.md (4096 tokens).
+GATE_UP_DRAM_TRAFFIC_BYTES = 2_321_533_184   # 1 659 791 360 read + 661 741 824 written
 
 
 def layer_flops(tokens, hidden, inter):
