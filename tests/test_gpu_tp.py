@@ -1,0 +1,66 @@
+"""Tensor-parallel layer over NCCL on two GPUs (skipped on a single-GPU box): each rank runs
+the rank-7 chain on its shard, one all-reduce combines the partials, and the result must match
+the unsharded layer and the functional reference."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    import sys
+    from pathlib import Path
+
+    repo = Path(__file__).resolve().parent.parent
+    sys.path[:0] = [str(repo / "writes-that-matter_b200"), str(repo)]
+    import torch.distributed as dist
+    from lcgemm import ops, tp
+    from lcgemm.layer import DenseMlpLayer, Rank7MlpLayer
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        g = torch.Generator().manual_seed(3)
+        m, h, i = 512, 512, 2048
+        mk = lambda shape, scale=1.0: (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).to(dev)
+        x, nw, wgu, wd = mk((m, h)), mk((h,), 0.01), mk((2 * i, h), 0.02), mk((h, i), 0.02)
+        gu_shard, d_shard = tp.shard_mlp_weights(wgu, wd, rank, world)
+        layer = tp.TensorParallelMlp(m, nw, gu_shard, d_shard, 1e-6)
+        out = layer(x).clone()
+        out2 = layer(x).clone()                       # buffers are reused: a second pass must agree
+        full = Rank7MlpLayer(m, nw, wgu, wd, 1e-6)(x)
+        dense = DenseMlpLayer(m, nw, wgu, wd, 1e-6, gemm="cublas")(x)
+        ops.check_status()
+        rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+        branch = lambda y: y.float() - x.float()
+        ret[rank] = (rel(out, full), rel(branch(out), branch(dense)), rel(out2, out))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_tensor_parallel_layer():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
+        assert len(ret) == 2
+        for rank in range(2):
+            vs_full, branch_vs_dense, repeat = ret[rank]
+            assert vs_full < 4e-3, (rank, vs_full)               # residual-dominated output
+            assert branch_vs_dense < 5e-2, (rank, branch_vs_dense)
+            assert repeat < 4e-3, (rank, repeat)
+        assert ret[0] == pytest.approx(ret[1], rel=0.5, abs=1e-3)
