@@ -533,8 +533,45 @@ def run_sweep(args, device):
             torch.cuda.empty_cache()
 
 
+def run_model(args, device):
+    """BASELINE config 3: batch-1 prefill of a random-init 64-layer dense decoder, stock MLP vs
+    rank-7 MLP, on seeded uniform-random prompts of 2048 / 4096 / 8192 tokens."""
+    from lcgemm import ops
+    from lcgemm.model import DecoderConfig, RandomInitDecoder, compare_arms
+
+    cfg = DecoderConfig(layers=args.layers)
+    model = RandomInitDecoder(cfg, device)
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.int8, device=device)
+    for tokens in (2048, 4096, 8192):
+        info = model.install(tokens)
+        ids = torch.randint(0, cfg.vocab, (tokens,), generator=torch.Generator().manual_seed(tokens)).to(device)
+        outs, times = {}, {"stock": [], "rank7": []}
+        for arm in times:
+            for _ in range(max(1, args.warmup - 2)):
+                outs[arm] = model.prefill(ids, arm=arm)
+        torch.cuda.synchronize()
+        before = dict(model.calls)
+        for _ in range(args.steps):
+            for arm in times:
+                times[arm] += _event_times(lambda: model.prefill(ids, arm=arm), 1, 0, flush)
+        ops.check_status()
+        fused = model.calls["fused"] - before["fused"]
+        st, r7 = statistics.median(times["stock"]), statistics.median(times["rank7"])
+        print(json.dumps({
+            "model": "random-init dense decoder", "layers": cfg.layers, "hidden": cfg.hidden,
+            "inter": cfg.inter, "heads": [cfg.q_heads, cfg.kv_heads, cfg.head_dim], "vocab": cfg.vocab,
+            "tokens": tokens, "passes": args.steps, "stock_ms": st, "rank7_ms": r7,
+            "speedup_pct": (st / r7 - 1.0) * 100.0, "fused_calls": fused,
+            "expected_fused_calls": args.steps * cfg.layers, "planes_gib": info["planes_gib"],
+            "agreement": compare_arms(outs["stock"][0], outs["rank7"][0], outs["stock"][1], outs["rank7"][1]),
+            "data": "synthetic: random-init weights (seed 0), uniform-random token ids"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--model", action="store_true",
+                    help="end-to-end prefill of the random-init decoder (BASELINE config 3)")
+    ap.add_argument("--layers", type=int, default=64, help="decoder layers for --model")
     ap.add_argument("--case", default=None,
                     help="time one kernel alone: gate_up | down | norm_planes | dense_gate_up")
     ap.add_argument("--tokens", type=int, default=4096, help="token count for --case")
@@ -558,14 +595,21 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the rank-7 path has no CPU implementation")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    if args.case or args.sweep:
+    if args.case or args.sweep or args.model:
         if world != 1:
-            raise SystemExit("--case / --sweep run on one GPU")
+            raise SystemExit("--case / --sweep / --model run on one GPU")
+        if args.model:
+            return run_model(args, device)
         return run_case(args, device) if args.case else run_sweep(args, device)
     if world > 1:
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; stdout carries the one
+        # JSON line of this run, so keep NCCL to warnings unless the caller asked for more.
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     try:
         run_ours(args, rank, world, device)

@@ -1,0 +1,35 @@
+"""End-to-end prefill of a small random-init decoder: the rank-7 MLP arm against the stock arm
+(everything but the MLP shared), with the agreement measures the reference gates on."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_small_decoder_arms_agree():
+    from lcgemm import ops
+    from lcgemm.model import DecoderConfig, RandomInitDecoder, compare_arms, tie_aware_overlap
+
+    cfg = DecoderConfig(layers=4, hidden=512, q_heads=8, kv_heads=2, head_dim=64, inter=1024,
+                        vocab=4096, seed=1)
+    model = RandomInitDecoder(cfg)
+    tokens = torch.randint(0, cfg.vocab, (512,), generator=torch.Generator().manual_seed(2)).cuda()
+    with pytest.raises(RuntimeError):
+        model.prefill(tokens, arm="rank7")
+    info = model.install(512)
+    assert info["layers"] == 4 and "rank7" in info["describe"]["gate_up"]
+    stock_logits, stock_hidden = model.prefill(tokens, arm="stock")
+    before = dict(model.calls)
+    r7_logits, r7_hidden = model.prefill(tokens, arm="rank7")
+    assert model.calls["fused"] - before["fused"] == cfg.layers
+    assert model.calls["reference"] == before["reference"]
+    dn_logits, dn_hidden = model.prefill(tokens, arm="dense")
+    ops.check_status()
+    cmp7 = compare_arms(stock_logits, r7_logits, stock_hidden, r7_hidden)
+    cmpd = compare_arms(stock_logits, dn_logits, stock_hidden, dn_hidden)
+    assert cmpd["hidden_rel_fro"] < 1e-2 and cmp7["hidden_rel_fro"] < 2e-2
+    assert cmp7["tie_aware_top20"] >= 19 and cmpd["tie_aware_top20"] >= 19
+    # top-1 may only differ where the stock arm's own top-2 gap is below the noise of a bf16 MLP
+    if not cmp7["top1_equal"]:
+        assert cmp7["top1_gap"] < 4 * cmp7["max_abs_logit_diff"]
+    assert tie_aware_overlap(stock_logits, stock_logits) == 20
