@@ -545,10 +545,11 @@ def run_model(args, device):
     for tokens in (2048, 4096, 8192):
         info = model.install(tokens)
         ids = torch.randint(0, cfg.vocab, (tokens,), generator=torch.Generator().manual_seed(tokens)).to(device)
-        outs, times = {}, {"stock": [], "rank7": []}
+        outs, times = {}, {"stock": [], "rank7": [], "dense": []}
         for arm in times:
             for _ in range(max(1, args.warmup - 2)):
                 outs[arm] = model.prefill(ids, arm=arm)
+        outs["eager"] = model.prefill(ids, arm="eager")
         torch.cuda.synchronize()
         before = dict(model.calls)
         for _ in range(args.steps):
@@ -556,14 +557,18 @@ def run_model(args, device):
                 times[arm] += _event_times(lambda: model.prefill(ids, arm=arm), 1, 0, flush)
         ops.check_status()
         fused = model.calls["fused"] - before["fused"]
-        st, r7 = statistics.median(times["stock"]), statistics.median(times["rank7"])
+        st, r7, dn = (statistics.median(times[a]) for a in ("stock", "rank7", "dense"))
+        cmp = lambda a, b: compare_arms(outs[a][0], outs[b][0], outs[a][1], outs[b][1])
         print(json.dumps({
             "model": "random-init dense decoder", "layers": cfg.layers, "hidden": cfg.hidden,
             "inter": cfg.inter, "heads": [cfg.q_heads, cfg.kv_heads, cfg.head_dim], "vocab": cfg.vocab,
-            "tokens": tokens, "passes": args.steps, "stock_ms": st, "rank7_ms": r7,
-            "speedup_pct": (st / r7 - 1.0) * 100.0, "fused_calls": fused,
+            "tokens": tokens, "passes": args.steps, "stock_ms": st, "rank7_ms": r7, "dense_tcgen05_ms": dn,
+            "speedup_pct": (st / r7 - 1.0) * 100.0, "speedup_vs_dense_tcgen05_pct": (dn / r7 - 1.0) * 100.0,
+            "fused_calls": fused,
             "expected_fused_calls": args.steps * cfg.layers, "planes_gib": info["planes_gib"],
-            "agreement": compare_arms(outs["stock"][0], outs["rank7"][0], outs["stock"][1], outs["rank7"][1]),
+            "agreement_rank7_vs_stock": cmp("stock", "rank7"),
+            "agreement_dense_tcgen05_vs_stock": cmp("stock", "dense"),
+            "agreement_eager_vs_stock": cmp("stock", "eager"),
             "data": "synthetic: random-init weights (seed 0), uniform-random token ids"}), flush=True)
 
 

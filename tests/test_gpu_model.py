@@ -24,6 +24,8 @@ def test_small_decoder_arms_agree():
     assert model.calls["fused"] - before["fused"] == cfg.layers
     assert model.calls["reference"] == before["reference"]
     dn_logits, dn_hidden = model.prefill(tokens, arm="dense")
+    eg_logits, eg_hidden = model.prefill(tokens, arm="eager")
+    assert compare_arms(stock_logits, eg_logits, stock_hidden, eg_hidden)["hidden_rel_fro"] < 1e-2
     ops.check_status()
     cmp7 = compare_arms(stock_logits, r7_logits, stock_hidden, r7_hidden)
     cmpd = compare_arms(stock_logits, dn_logits, stock_hidden, dn_hidden)

@@ -10,10 +10,14 @@ every line of code except the MLP, so a difference in the output is the MLP's al
 
 Arms of :meth:`RandomInitDecoder.prefill`:
 
-``"stock"``   the functional MLP of the stock layer on cuBLAS (``qwen_patch.py:41-58``);
+``"stock"``   the stock layer as an engine runs it: fused add + RMSNorm kernel, cuBLAS GEMMs,
+              fused SwiGLU kernel (the rounding points of ``qwen_patch.py:41-58``);
+``"eager"``   the same layer as plain torch ops, the functional reference itself;
 ``"rank7"``   the chained rank-7 plans of this package (one ``build_chain`` for the model, B
               planes prepared per layer at :meth:`install`, as ``qwen_patch._prepare`` does);
 ``"dense"``   the stock layer on this package's dense tcgen05 GEMM.
+
+The input norm of every layer uses the fused add + RMSNorm kernel in all arms.
 """
 from __future__ import annotations
 
@@ -109,20 +113,25 @@ class RandomInitDecoder:
                  residual_out=res_out)
             return down(prepared_w=layer["down_bw"]), res_out
         self.calls["reference"] += 1
-        h = (delta.float() + residual.float()).to(delta.dtype)
-        x = _rmsnorm(h, layer["post_norm"], cfg.eps)
+        if arm == "eager":
+            h = (delta.float() + residual.float()).to(delta.dtype)
+            x = _rmsnorm(h, layer["post_norm"], cfg.eps)
+            gate_, up = F.linear(x, layer["gate_up"]).chunk(2, dim=-1)
+            act = F.silu(gate_.float()).to(gate_.dtype) * up
+            return F.linear(act, layer["down"]), h
+        h = ring[0]
+        ring.reverse()
+        x, _ = ops.add_rmsnorm(delta, residual, layer["post_norm"], cfg.eps, residual_out=h)
         if arm == "dense":
             z = ops.gemm_dense(x, layer["gate_up"])
             return ops.gemm_dense(ops.swiglu(z), layer["down"]), h
-        gate_, up = F.linear(x, layer["gate_up"]).chunk(2, dim=-1)
-        act = F.silu(gate_.float()).to(gate_.dtype) * up
-        return F.linear(act, layer["down"]), h
+        return F.linear(ops.swiglu(F.linear(x, layer["gate_up"])), layer["down"]), h
 
     # ---------------------------------------------------------------------- forward
     @torch.no_grad()
     def prefill(self, token_ids: torch.Tensor, arm: str = "stock"):
         """Batch-1 prefill; returns (logits of the last position as fp32, final hidden state)."""
-        if arm not in ("stock", "rank7", "dense"):
+        if arm not in ("stock", "eager", "rank7", "dense"):
             raise ValueError(f"unknown arm {arm!r}")
         cfg = self.cfg
         m = token_ids.shape[0]
@@ -142,8 +151,7 @@ class RandomInitDecoder:
                 residual = hidden
                 x = _rmsnorm(hidden, layer["input_norm"], cfg.eps)
             else:
-                residual = (hidden.float() + residual.float()).to(hidden.dtype)
-                x = _rmsnorm(residual, layer["input_norm"], cfg.eps)
+                x, residual = ops.add_rmsnorm(hidden.contiguous(), residual, layer["input_norm"], cfg.eps)
             qkv = F.linear(x, layer["qkv"])
             q = _rope(qkv[:, :q_dim].view(m, cfg.q_heads, cfg.head_dim), cos, sin)
             k = _rope(qkv[:, q_dim:q_dim + kv_dim].view(m, cfg.kv_heads, cfg.head_dim), cos, sin)
