@@ -489,13 +489,11 @@ def run_sweep(args, device):
     """BASELINE config 5: bare rank-7 GEMM (A planes + GEMM, B planes prepared offline) against
     the dense tcgen05 GEMM and cuBLAS, odd shapes included, one JSON line per shape."""
     from lcgemm import ops, scheme as S
-    from lcgemm.seams.down import wants_rank_split
 
     flush = torch.empty(FLUSH_BYTES, dtype=torch.int8, device=device)
     for m in (2048, 4096, 8192):
         for k, n in SWEEP_KN:
-            split = wants_rank_split((m, k, n))
-            sch = S.load("2x2_locality_ordered" if split else "2x2_postsum_cse")
+            sch = S.load("2x2_postsum_cse")
             g = torch.Generator(device=device).manual_seed(m + k + n)
             a = torch.randn((m, k), generator=g, device=device).to(torch.bfloat16)
             w = (torch.randn((n, k), generator=g, device=device) * 0.02).to(torch.bfloat16)
@@ -505,7 +503,7 @@ def run_sweep(args, device):
             out = torch.empty((m, ld), device=device, dtype=torch.bfloat16)[:, :n]
             cb_out = torch.empty((m, n), device=device, dtype=torch.bfloat16)
             arms = {
-                "rank7": lambda: ops.gemm_r7(a, bp, n, sch, out=out, a_workspace=ws, schedule=int(split)),
+                "rank7": lambda: ops.gemm_r7(a, bp, n, sch, out=out, a_workspace=ws),
                 "dense_tcgen05": lambda: ops.gemm_dense(a, w, out=out),
                 "dense_cublas": lambda: torch.matmul(a, w.t(), out=cb_out),
             }
@@ -522,7 +520,7 @@ def run_sweep(args, device):
             fl = 2.0 * m * n * k
             print(json.dumps({
                 "sweep": "bare_gemm", "M": m, "K": k, "N": n,
-                "schedule": "rank_split" if split else "all_ranks", "scheme": sch.name,
+                "schedule": "hybrid", "scheme": sch.name,
                 "rank7_ms": r7, "dense_tcgen05_ms": dn, "dense_cublas_ms": cb,
                 "rank7_effective_tflops": fl / r7 / 1e9, "rank7_executed_tflops": 0.875 * fl / r7 / 1e9,
                 "dense_tcgen05_tflops": fl / dn / 1e9, "dense_cublas_tflops": fl / cb / 1e9,

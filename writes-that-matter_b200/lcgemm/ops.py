@@ -154,10 +154,12 @@ def gemm_dense(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None
 
 
 def gemm_r7_planes(scheme, a_pl: torch.Tensor, b_pl: torch.Tensor, m: int, n: int, k: int,
-                   out: torch.Tensor | None = None, schedule: int = nat.SCHEDULE_ALL_RANKS,
+                   out: torch.Tensor | None = None, schedule: int = nat.SCHEDULE_HYBRID,
                    cta_group: int = 0, zero_out: bool = True) -> torch.Tensor:
-    """Rank-7 ``C = A @ B^T`` from prepared planes.  With the rank-split schedule the output
-    must arrive zeroed; ``zero_out`` does that here with a memset on the stream."""
+    """Rank-7 ``C = A @ B^T`` from prepared planes.  The default hybrid schedule walks whole
+    waves of tiles product by product and splits the last partial wave by product (for a shape
+    with fewer tiles than CTA groups that is all of it).  With the pure rank-split schedule the
+    output must arrive zeroed; ``zero_out`` does that here with a memset on the stream."""
     _need(a_pl, "A planes"), _need(b_pl, "B planes")
     if tuple(a_pl.shape) != a_plane_shape(scheme, m, k):
         raise ValueError(f"A planes must be {a_plane_shape(scheme, m, k)}, got {tuple(a_pl.shape)}")
@@ -177,7 +179,7 @@ def gemm_r7_planes(scheme, a_pl: torch.Tensor, b_pl: torch.Tensor, m: int, n: in
 
 
 def gemm_r7(a: torch.Tensor, b_pl: torch.Tensor, n: int, scheme, out: torch.Tensor | None = None,
-            a_workspace: torch.Tensor | None = None, schedule: int = nat.SCHEDULE_ALL_RANKS,
+            a_workspace: torch.Tensor | None = None, schedule: int = nat.SCHEDULE_HYBRID,
             cta_group: int = 0) -> torch.Tensor:
     """Bare rank-7 GEMM: form the A planes of ``a (M, K)``, then multiply with prepared B planes."""
     m, k = a.shape
