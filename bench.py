@@ -472,6 +472,10 @@ def run_case(args, device):
         else:
             down_bw = down.prepare_weight(wd)
             fn, flops = (lambda: down(prepared_w=down_bw)), 2.0 * m * i * h
+    elif args.case == "a_planes":
+        s_tok = torch.randn((m, i), device=device).to(torch.bfloat16)       # a down-shaped activation
+        ws = torch.empty(ops.a_plane_shape(down.scheme, m, i), device=device, dtype=torch.bfloat16)
+        fn, flops = (lambda: ops.a_planes(s_tok, down.scheme, out=ws)), 0.0
     elif args.case == "dense_gate_up":
         out = torch.empty((m, 2 * i), device=device, dtype=torch.bfloat16)
         fn, flops = (lambda: ops.gemm_dense(x, wgu, out=out)), 2.0 * m * h * 2 * i
@@ -576,7 +580,7 @@ def main():
                     help="end-to-end prefill of the random-init decoder (BASELINE config 3)")
     ap.add_argument("--layers", type=int, default=64, help="decoder layers for --model")
     ap.add_argument("--case", default=None,
-                    help="time one kernel alone: gate_up | down | norm_planes | dense_gate_up")
+                    help="time one kernel alone: gate_up | down | norm_planes | a_planes | dense_gate_up")
     ap.add_argument("--tokens", type=int, default=4096, help="token count for --case")
     ap.add_argument("--sweep", action="store_true", help="bare-GEMM shape sweep (BASELINE config 5)")
     ap.add_argument("--gpus", type=int, default=1)

@@ -65,7 +65,7 @@ def test_fused_epilogue_equals_unfused_kernels(lc, group, dims):
     pl = torch.full((7 * m // 2, i // 2), 3.0, device="cuda", dtype=torch.bfloat16)
     pc = torch.ones((m, 520), device="cuda", dtype=torch.bfloat16)
     lc.ops.gate_up_chain(gs, ds, ap, bp, z, pl, preclear=pc, schedule=0, cta_group=group)
-    z_plain = lc.ops.gemm_r7_planes(gs, ap, bp, m, 2 * i, h, cta_group=group)
+    z_plain = lc.ops.gemm_r7_planes(gs, ap, bp, m, 2 * i, h, schedule=0, cta_group=group)
     assert torch.equal(z, z_plain)                          # all-ranks schedule: deterministic
     assert torch.equal(pl, lc.gauge.chain_a_planes(z, ds))
     assert bool((pc == 0).all())
