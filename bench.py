@@ -374,7 +374,7 @@ def run_ours(args, rank, world, device):
     il = cfg["inter"] // world
     x, nw, wgu, wd = make_layer_tensors(cfg["tokens"], cfg["hidden"], cfg["inter"], device,
                                         inter_local=il, rank=rank)
-    layer = TensorParallelMlp(cfg["tokens"], nw, wgu, wd, EPS)
+    layer = TensorParallelMlp(cfg["tokens"], nw, wgu, wd, EPS, slabs=args.slabs)
     launches0 = ops.launch_count()
     with ClockWatch(torch.cuda.current_device()) as cw:
         times = timed_steps(lambda: layer(x), args.steps, args.warmup, flush, sync_all,
@@ -405,6 +405,7 @@ def run_ours(args, rank, world, device):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": _workload_name(world), **cfg, "parallelism": f"tp{world}",
+                       "down_slabs": args.slabs,
                        "all_reduce_bytes": cfg["tokens"] * cfg["hidden"] * 2,
                        "l2": "flushed between steps (256 MiB memset)"},
             "clocks": cw.summary(),
@@ -587,6 +588,8 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--slabs", type=int, default=4,
+                    help="N > 1: slabs of the down GEMM pipelined with the all-reduce (1 = no overlap)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -617,6 +620,7 @@ def main():
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        os.environ.setdefault("NCCL_MAX_CTAS", "16")     # the pipelined down GEMM leaves 16 SMs free
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     try:
         run_ours(args, rank, world, device)

@@ -157,6 +157,19 @@ int lcg_gemm_r7(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,
                 int64_t M, int64_t N, int64_t K, int schedule, int cta_group,
                 int32_t* status, void* stream);
 
+/* lcg_gemm_r7 restricted to the tile rows [tile_row_begin, tile_row_end) of both block rows
+ * (a tile row is 128 * cta_group rows of a block row: output rows i * M2 + [begin, end) * 256
+ * for i = 0, 1 with the default pairing; tile_row_end < 0 means "to the last"), on at most
+ * `max_groups` CTA groups (0 = all SMs).  This is how the tensor-parallel layer pipelines the
+ * row-parallel `down` GEMM with the all-reduce of the slab before it: the slabs run back to
+ * back on the compute stream while NCCL reduces finished slabs on the SMs left free.  No
+ * counterpart in the reference, which is single-GPU (lcgemm/integrate/qwen_patch.py:216-217). */
+int lcg_gemm_r7_slab(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,
+                     const void* b_planes, int64_t ld_b, void* c, int64_t ldc,
+                     int64_t M, int64_t N, int64_t K, int schedule, int cta_group,
+                     int tile_row_begin, int tile_row_end, int max_groups,
+                     int32_t* status, void* stream);
+
 /* The chained gate_up GEMM (lcgemm/kernels/sm100.py `LcGemmSm100.call_planes`):
  * Z = rank-7 product into z (M, N = 2*I), then, in the same kernel, one tile
  * behind the mainloop, S = silu(Z[:, :I]) * Z[:, I:] and the consumer's A planes

@@ -33,19 +33,22 @@ def _worker(rank, world, port, ret):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         g = torch.Generator().manual_seed(3)
-        m, h, i = 512, 512, 2048
+        m, h, i = 1024, 512, 2048
         mk = lambda shape, scale=1.0: (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).to(dev)
         x, nw, wgu, wd = mk((m, h)), mk((h,), 0.01), mk((2 * i, h), 0.02), mk((h, i), 0.02)
         gu_shard, d_shard = tp.shard_mlp_weights(wgu, wd, rank, world)
         layer = tp.TensorParallelMlp(m, nw, gu_shard, d_shard, 1e-6)
         out = layer(x).clone()
         out2 = layer(x).clone()                       # buffers are reused: a second pass must agree
+        piped = tp.TensorParallelMlp(m, nw, gu_shard, d_shard, 1e-6, slabs=2)
+        out3 = piped(x).clone()                       # down in two slabs, all-reduce overlapped
+        out3 = piped(x).clone()
         full = Rank7MlpLayer(m, nw, wgu, wd, 1e-6)(x)
         dense = DenseMlpLayer(m, nw, wgu, wd, 1e-6, gemm="cublas")(x)
         ops.check_status()
         rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
         branch = lambda y: y.float() - x.float()
-        ret[rank] = (rel(out, full), rel(branch(out), branch(dense)), rel(out2, out))
+        ret[rank] = (rel(out, full), rel(branch(out), branch(dense)), rel(out2, out), rel(out3, out))
     finally:
         dist.destroy_process_group()
 
@@ -59,7 +62,8 @@ def test_two_gpu_tensor_parallel_layer():
         mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
         assert len(ret) == 2
         for rank in range(2):
-            vs_full, branch_vs_dense, repeat = ret[rank]
+            vs_full, branch_vs_dense, repeat, piped = ret[rank]
+            assert piped < 4e-3, (rank, piped)
             assert vs_full < 4e-3, (rank, vs_full)               # residual-dominated output
             assert branch_vs_dense < 5e-2, (rank, branch_vs_dense)
             assert repeat < 4e-3, (rank, repeat)

@@ -94,6 +94,8 @@ struct GemmParams {
   int32_t main_tiles;         // tiles walked whole; the remaining tail_tiles are split by product
   int32_t tail_tiles;         //   (hybrid schedule; 0 otherwise): unit = main + product * tail + n
   int32_t tiles_m, tiles_n, group_m;
+  int32_t tm_base;            // first tile row of this launch (a slab of tile rows; 0 = from the top)
+  int32_t max_groups;         // cap on CTA groups (0 = all SMs); leaves SMs to a concurrent kernel
   int32_t num_units;
   int32_t k_blocks;
   int32_t a_plane_rows, b_plane_rows;
@@ -117,7 +119,7 @@ __device__ __forceinline__ void tile_coord(const GemmParams& p, int t, int& tm, 
   const int band = t / band_sz;
   const int rem = t - band * band_sz;
   const int gm = min(p.group_m, p.tiles_m - band * p.group_m);
-  tm = band * p.group_m + rem % gm;
+  tm = p.tm_base + band * p.group_m + rem % gm;
   tn = rem / gm;
 }
 __device__ __forceinline__ UnitCoord decode_unit(const GemmParams& p, int u) {
@@ -641,7 +643,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CMaps& mc, GemmPa
     LCG_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes));
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  const int max_groups = sm_count() / kCtaGroup;
+  int max_groups = sm_count() / kCtaGroup;
+  if (p.max_groups > 0 && p.max_groups < max_groups) max_groups = p.max_groups;
   const int groups = p.num_units < max_groups ? p.num_units : max_groups;
   if (kChain) p.chain.iters_max = (p.num_units + groups - 1) / groups;
   cudaLaunchConfig_t cfg = {};
@@ -686,7 +689,7 @@ int r7_geometry(int64_t M, int64_t N, int64_t K, R7Geometry* g) {
 int fill_r7(const lcg_scheme* scheme, const void* a_planes, int64_t ld_a, const void* b_planes,
             int64_t ld_b, void* c, int64_t ldc, int64_t M, int64_t N, const R7Geometry& g,
             int schedule, int cta_group, CUtensorMap* ma, CUtensorMap* mb, CMaps* mc,
-            GemmParams* p) {
+            GemmParams* p, int tm_begin = 0, int tm_end = -1, int max_groups = 0) {
   const int tile_m = kBM * cta_group;
   if (int e = make_map(ma, a_planes, g.k2p, scheme->rank * g.m2, ld_a, kBM, "A planes")) return e;
   if (int e = make_map(mb, b_planes, g.k2p, scheme->rank * g.n2, ld_b, kBN / cta_group, "B planes"))
@@ -707,9 +710,16 @@ int fill_r7(const lcg_scheme* scheme, const void* a_planes, int64_t ld_a, const 
   }
   p->steps_per_unit = scheme->rank;
   p->rank_split = split ? 1 : 0;
-  p->tiles_m = static_cast<int>((g.m2 + tile_m - 1) / tile_m);
+  const int tiles_m_all = static_cast<int>((g.m2 + tile_m - 1) / tile_m);
+  if (tm_end < 0) tm_end = tiles_m_all;
+  if (tm_begin < 0 || tm_begin >= tm_end || tm_end > tiles_m_all)
+    return fail(LCG_ERR_BAD_ARG, "tile-row slab [%d, %d) outside [0, %d)", tm_begin, tm_end, tiles_m_all);
+  p->tm_base = tm_begin;
+  p->tiles_m = tm_end - tm_begin;
   p->tiles_n = static_cast<int>((g.n2 + kBN - 1) / kBN);
-  const int groups = sm_count() / cta_group;
+  int groups = sm_count() / cta_group;
+  if (max_groups > 0 && max_groups < groups) groups = max_groups;
+  p->max_groups = max_groups;
   p->group_m = pick_group_m(p->tiles_m, groups);
   const int tiles = p->tiles_m * p->tiles_n;
   p->main_tiles = tiles;
@@ -815,6 +825,33 @@ extern "C" int lcg_gemm_r7(const lcg_scheme_t* scheme, const void* a_planes, int
   GemmParams p;
   if (int e = fill_r7(scheme, a_planes, ld_a, b_planes, ld_b, c, ldc, M, N, g, schedule, cta_group,
                       &ma, &mb, &mc, &p))
+    return e;
+  p.status = status;
+  auto st_ = static_cast<cudaStream_t>(stream);
+  if (int e = zero_tail_tiles(p, c, ldc, M, N, g, cta_group, st_)) return e;
+  return cta_group == 1 ? launch<1, false>(ma, mb, mc, p, st_) : launch<2, false>(ma, mb, mc, p, st_);
+}
+
+extern "C" int lcg_gemm_r7_slab(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,
+                                const void* b_planes, int64_t ld_b, void* c, int64_t ldc, int64_t M,
+                                int64_t N, int64_t K, int schedule, int cta_group, int tile_row_begin,
+                                int tile_row_end, int max_groups, int32_t* status, void* stream) {
+  if (!scheme || !a_planes || !b_planes || !c) return fail(LCG_ERR_BAD_ARG, "NULL operand");
+  if (schedule != LCG_SCHEDULE_ALL_RANKS && schedule != LCG_SCHEDULE_RANK_SPLIT &&
+      schedule != LCG_SCHEDULE_HYBRID)
+    return fail(LCG_ERR_BAD_ARG, "unknown schedule %d", schedule);
+  cta_group = resolve_group(cta_group);
+  if (cta_group != 1 && cta_group != 2) return fail(LCG_ERR_BAD_ARG, "cta_group must be 0, 1 or 2");
+  if (max_groups < 0) return fail(LCG_ERR_BAD_ARG, "max_groups must be >= 0");
+  R7Geometry g;
+  if (int e = r7_geometry(M, N, K, &g)) return e;
+  if (ldc < N) return fail(LCG_ERR_BAD_ARG, "ldc below N");
+  if (ld_a < g.k2p || ld_b < g.k2p) return fail(LCG_ERR_BAD_ARG, "plane leading dimension below K2p");
+  CUtensorMap ma, mb;
+  CMaps mc;
+  GemmParams p;
+  if (int e = fill_r7(scheme, a_planes, ld_a, b_planes, ld_b, c, ldc, M, N, g, schedule, cta_group,
+                      &ma, &mb, &mc, &p, tile_row_begin, tile_row_end, max_groups))
     return e;
   p.status = status;
   auto st_ = static_cast<cudaStream_t>(stream);

@@ -178,6 +178,18 @@ def gemm_r7_planes(scheme, a_pl: torch.Tensor, b_pl: torch.Tensor, m: int, n: in
     return out
 
 
+def gemm_r7_slab(scheme, a_pl, b_pl, m: int, n: int, k: int, out: torch.Tensor, tile_rows,
+                 schedule: int = nat.SCHEDULE_RANK_SPLIT, max_groups: int = 0, cta_group: int = 0) -> None:
+    """The tile rows ``[tile_rows[0], tile_rows[1])`` of the rank-7 product into ``out`` (whole
+    ``(m, n)`` output buffer; rank-split slabs accumulate, so it arrives zeroed), on at most
+    ``max_groups`` CTA groups."""
+    _need(a_pl, "A planes"), _need(b_pl, "B planes"), _need(out, "out")
+    check(lib().lcg_gemm_r7_slab(NativeScheme.of(scheme).handle, ptr(a_pl), a_pl.stride(0), ptr(b_pl),
+                                 b_pl.stride(0), ptr(out), out.stride(0), m, n, k, schedule, cta_group,
+                                 int(tile_rows[0]), int(tile_rows[1]), max_groups,
+                                 ptr(status_word(a_pl.device)), stream_ptr()))
+
+
 def gemm_r7(a: torch.Tensor, b_pl: torch.Tensor, n: int, scheme, out: torch.Tensor | None = None,
             a_workspace: torch.Tensor | None = None, schedule: int = nat.SCHEDULE_HYBRID,
             cta_group: int = 0) -> torch.Tensor:

@@ -80,6 +80,31 @@ class DownPlan:
             cta_group=self.cta_group, zero_out=self.rank_split and not cleared_by_producer)
         return c
 
+    # ------------------------------------------------------- slabs (tensor parallel)
+    TILE_ROWS = 256          # rows of a block row per tile row (2-CTA pairing)
+
+    @property
+    def tile_rows(self) -> int:
+        """Tile rows of one block row of the output."""
+        return -(-((self.shape[0] + 1) // 2) // self.TILE_ROWS)
+
+    def slab_rows(self, tile_range):
+        """The two output row ranges (one per block row) a slab of tile rows covers."""
+        m2 = (self.shape[0] + 1) // 2
+        t0, t1 = tile_range
+        return [(i * m2 + t0 * self.TILE_ROWS, min(i * m2 + t1 * self.TILE_ROWS, min((i + 1) * m2, self.shape[0])))
+                for i in range(2)]
+
+    def gemm_slab(self, a_planes, prepared_w, tile_range, *, max_groups: int = 0) -> torch.Tensor:
+        """The tile rows ``tile_range`` of the product into ``self.c`` (which a rank-split plan
+        expects zeroed, as the chained producer leaves it); used to pipeline ``down`` with the
+        all-reduce of the previous slab."""
+        m, k, n = self.shape
+        ops.gemm_r7_slab(self.scheme, a_planes, prepared_w, m, n, k, self.c, tile_range,
+                         schedule=SCHEDULE_RANK_SPLIT if self.rank_split else SCHEDULE_ALL_RANKS,
+                         max_groups=max_groups, cta_group=2)
+        return self.c
+
     def __call__(self, *, prepared_w, out=None):
         return self.gemm(self.a_planes(), prepared_w, out=out)
 

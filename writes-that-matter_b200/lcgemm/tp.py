@@ -9,9 +9,15 @@ multi-GPU form of the same layer.  Rank ``g`` of ``tp`` holds
 * ``down`` shard ``W_down[:, g*I/tp:(g+1)*I/tp]`` -- row parallel.
 
 Each rank runs the whole rank-7 chain on its shard with no communication (the input is
-replicated), producing a partial ``(M, H)`` output; one all-reduce (NCCL over
+replicated), producing a partial ``(M, H)`` output; an all-reduce (NCCL over
 NVLink/NVSwitch, bf16 sum) per layer combines the partials, and the residual is added after
 the reduction.  One process per GPU; ``torch.distributed`` provides the process group.
+
+With ``slabs > 1`` the row-parallel ``down`` GEMM is issued as that many slabs of tile rows and
+the all-reduce of each finished slab (two row ranges, one per block row) runs asynchronously
+while the next slab computes; the GEMM then leaves ``reserve_groups`` CTA pairs' worth of SMs
+free, because one of its CTAs fills an SM's shared memory and NCCL's kernels could not start
+beside it.
 """
 from __future__ import annotations
 
@@ -50,7 +56,7 @@ class TensorParallelMlp:
     """
 
     def __init__(self, tokens: int, norm_weight, gate_up_shard, down_shard, eps: float = 1e-6,
-                 group=None, make_layer=None, add=None):
+                 group=None, make_layer=None, add=None, slabs: int = 1, reserve_groups: int = 8):
         if make_layer is None:
             from .layer import Rank7MlpLayer as make_layer
         self.group = group
@@ -58,12 +64,16 @@ class TensorParallelMlp:
         self._add = add
         self._zero = None
         self.out = None
+        self.slabs = max(1, int(slabs))
+        self.reserve_groups = reserve_groups
 
     def forward(self, x: torch.Tensor, delta: torch.Tensor | None = None) -> torch.Tensor:
         if delta is None:
             if self._zero is None or self._zero.shape != x.shape:
                 self._zero = torch.zeros_like(x)
             delta = self._zero
+        if self.slabs > 1 and hasattr(self.layer, "down_plan") and self.layer.down_plan.c.is_contiguous():
+            return self._forward_pipelined(x, delta)
         partial, h = self.layer.chain(delta, x)
         if not partial.is_contiguous():
             partial = partial.contiguous()
@@ -76,6 +86,35 @@ class TensorParallelMlp:
             if self.out is None or self.out.shape != h.shape:
                 self.out = torch.empty_like(h)
             ops.add(h, partial, out=self.out)
+        return self.out
+
+    def _forward_pipelined(self, x, delta):
+        from . import ops
+
+        lay = self.layer
+        gate, down = lay.gate_plan, lay.down_plan
+        gate(x, delta, lay.norm_weight, lay.eps, prepared_w=lay.gate_bw)   # also zeroes down.c
+        h = gate.residual_out
+        if down.rank_split and gate.preclear is not down.c:
+            down.c.zero_()
+        total = down.tile_rows
+        slabs = min(self.slabs, total)
+        edges = [round(s * total / slabs) for s in range(slabs + 1)]
+        distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1
+        max_groups = max(1, 74 - self.reserve_groups) if distributed else 0
+        pending = []
+        for s in range(slabs):
+            down.gemm_slab(down.a_planes(), lay.down_bw, (edges[s], edges[s + 1]), max_groups=max_groups)
+            if distributed:
+                for r0, r1 in down.slab_rows((edges[s], edges[s + 1])):
+                    if r1 > r0:
+                        pending.append(dist.all_reduce(down.c[r0:r1], op=dist.ReduceOp.SUM,
+                                                       group=self.group, async_op=True))
+        for work in pending:
+            work.wait()
+        if self.out is None or self.out.shape != h.shape:
+            self.out = torch.empty_like(h)
+        ops.add(h, down.c, out=self.out)
         return self.out
 
     __call__ = forward
