@@ -588,7 +588,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    ap.add_argument("--slabs", type=int, default=4,
+    ap.add_argument("--slabs", type=int, default=1,
                     help="N > 1: slabs of the down GEMM pipelined with the all-reduce (1 = no overlap)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -620,7 +620,6 @@ def main():
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        os.environ.setdefault("NCCL_MAX_CTAS", "16")     # the pipelined down GEMM leaves 16 SMs free
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     try:
         run_ours(args, rank, world, device)
