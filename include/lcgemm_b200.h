@@ -242,6 +242,12 @@ int lcg_reset_state(void* stream);
  * `gpu_launches`). */
 int64_t lcg_launch_count(void);
 
+/* Exercise the bounded device-side wait: a one-CTA kernel waits (for at most limit_us
+ * microseconds) on a barrier nothing signals, so the wait runs out, writes code 199 into
+ * `status` and the kernel returns; `finished` (device int32, may be NULL) receives 1.  Shows
+ * a host how a stuck pipeline surfaces: as a status code, never as a hung context. */
+int lcg_selftest_wait_timeout(int32_t* status, int64_t limit_us, int32_t* finished, void* stream);
+
 /* One line describing the schedule the GEMM entry points would pick for a
  * shape (tile, stages, units, CTA groups); the counterpart of the reference's
  * Plan.describe() (lcgemm/kernels/sm100.py:358-374). Returns bytes written. */

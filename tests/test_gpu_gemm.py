@@ -142,3 +142,20 @@ def test_full_size_properties(lc, name, schedule, shape):
     lhs = c.float() @ ones
     rhs = a.float() @ (w.float().T @ ones)
     assert rel_fro(lhs, rhs) < 2e-2
+
+
+def test_bounded_wait_reports_instead_of_hanging(lc):
+    """A wait nothing satisfies runs out after its limit, leaves its code in the status word
+    and the kernel returns; the context keeps working and check_status raises."""
+    word = lc.ops.status_word()
+    word.zero_()
+    finished = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    lc.nat.check(lc.nat.lib().lcg_selftest_wait_timeout(word.data_ptr(), 2000, finished.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert finished.item() == 1 and word[0].item() == 199
+    with pytest.raises(RuntimeError, match="wait ran out"):
+        lc.ops.check_status()
+    assert word[0].item() == 0                              # cleared for the next launch
+    a, b = seeded((128, 64), 1), seeded((256, 64), 2, 0.02)
+    assert rel_fro(lc.ops.gemm_dense(a, b), a.double().cpu() @ b.double().cpu().T) <= TOL_DENSE

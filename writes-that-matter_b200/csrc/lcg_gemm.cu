@@ -958,3 +958,37 @@ extern "C" int lcg_reset_state(void* stream) {
                               static_cast<cudaStream_t>(stream)));
   return LCG_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Self-test of the bounded-wait machinery: one CTA waits on an mbarrier that nothing ever
+// arrives at, with a short limit.  The wait must run out, record `kCodeSelfTest` in the status
+// word and let the kernel return normally; the context stays usable.
+namespace lcg {
+constexpr int kCodeSelfTest = 199;
+__global__ void k_selftest_wait(int32_t* status, uint64_t limit_ns, int* finished) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0u;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  WaitCtl ctl{&abort_flag, status, limit_ns};
+  mbar_wait(smem_u32(&bar), 0u, ctl, kCodeSelfTest);     // phase 0 never completes
+  mbar_wait(smem_u32(&bar), 0u, ctl, kCodeSelfTest);     // a later wait returns at once
+  __syncthreads();
+  if (threadIdx.x == 0 && finished != nullptr) *finished = abort_flag != 0u ? 1 : 0;
+}
+}  // namespace lcg
+
+extern "C" int lcg_selftest_wait_timeout(int32_t* status, int64_t limit_us, int32_t* finished,
+                                         void* stream) {
+  if (status == nullptr) return fail(LCG_ERR_BAD_ARG, "status must not be NULL");
+  if (limit_us < 1 || limit_us > 1000000) return fail(LCG_ERR_BAD_ARG, "limit_us outside [1, 1e6]");
+  k_selftest_wait<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(
+      status, static_cast<uint64_t>(limit_us) * 1000ull, finished);
+  LCG_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return LCG_OK;
+}

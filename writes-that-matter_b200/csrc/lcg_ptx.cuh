@@ -94,12 +94,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // memory; once any wait of the CTA has run out it is set and every later wait
 // returns at once, so the kernel's control flow (loop trip counts, named
 // barriers) stays what it is in a healthy run and the kernel ends by itself.
+constexpr uint64_t kWaitLimitNs = 1500ull * 1000ull * 1000ull;  // 1.5 s per wait
+
 struct WaitCtl {
   volatile uint32_t* abort_flag;
   int32_t* status;  // device status word, may be null
+  uint64_t limit_ns = kWaitLimitNs;
 };
-
-constexpr uint64_t kWaitLimitNs = 1500ull * 1000ull * 1000ull;  // 1.5 s per wait
 
 __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtl& ctl,
                                             int code) {
@@ -109,7 +110,7 @@ __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, const
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xffu) == 0) {
       if (*ctl.abort_flag) return;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > ctl.limit_ns) {
         *ctl.abort_flag = 1u;
         if (ctl.status != nullptr) atomicCAS(ctl.status, 0, code);
         return;
@@ -144,7 +145,7 @@ __device__ __noinline__ void counter_wait(uint32_t addr, uint32_t at_least, cons
     __nanosleep(256);
     if ((++spins & 0xffu) == 0) {
       if (*ctl.abort_flag) return;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > ctl.limit_ns) {
         *ctl.abort_flag = 1u;
         if (ctl.status != nullptr) atomicCAS(ctl.status, 0, code);
         return;
