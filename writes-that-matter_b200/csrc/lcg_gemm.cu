@@ -80,7 +80,7 @@ struct ChainParams {
   int32_t plane_rank;
   int32_t iters_max;          // most work units any CTA group walks
   int32_t sched_slot;         // which row of g_tail_counters this launch uses
-  int32_t plane_steps_total;  // products per tile (arrivals that complete a tail tile)
+  int32_t plane_steps_total;  // weight that completes a tail tile: products per tile * ksplit
   TermTable plane_terms;
   uint4* preclear;            // consumer output to zero, or null
   int64_t preclear_vecs;
@@ -90,9 +90,17 @@ struct GemmParams {
   StepDesc steps[kMaxRank];        // whole-tile walk: chain plan, store-first scatter (or the dense step)
   StepDesc steps_split[kMaxRank];  // one product alone, reduce-add only
   int32_t steps_per_unit;     // steps of a whole-tile unit: 7, or 1 (dense)
-  int32_t rank_split;         // every unit is one product: unit = product * tiles + tile
-  int32_t main_tiles;         // tiles walked whole; the remaining tail_tiles are split by product
-  int32_t tail_tiles;         //   (hybrid schedule; 0 otherwise): unit = main + product * tail + n
+  // Unit list: [0, main_tiles) whole tiles; then single-product units over the tail_tiles tiles
+  // that follow (product-major: q = product * tail_tiles + n), the first full_units of them over
+  // the whole K, the remaining split_units each cut into ksplit K ranges (part-major).
+  // All-ranks: tail_tiles = 0.  Rank split: main_tiles = 0, tail_tiles = all tiles (and C arrives
+  // zeroed by the caller; `zero_tail` = 0).  Hybrid: both parts, tail zeroed by k_zero_tail_tiles.
+  int32_t main_tiles;
+  int32_t tail_tiles;
+  int32_t full_units;
+  int32_t split_units;
+  int32_t ksplit;
+  int32_t zero_tail;
   int32_t tiles_m, tiles_n, group_m;
   int32_t tm_base;            // first tile row of this launch (a slab of tile rows; 0 = from the top)
   int32_t max_groups;         // cap on CTA groups (0 = all SMs); leaves SMs to a concurrent kernel
@@ -112,6 +120,8 @@ struct UnitCoord {
   int split;           // 1: steps_split (single product, reduce-add), 0: steps
   int tile;            // linear tile index
   int tail;            // index among the tail tiles, or -1
+  int kb0, kb1;        // K blocks [kb0, kb1) of every step of the unit
+  int weight;          // arrivals this unit counts for in its tail tile's completion counter
   int tm, tn;
 };
 __device__ __forceinline__ void tile_coord(const GemmParams& p, int t, int& tm, int& tn) {
@@ -124,22 +134,28 @@ __device__ __forceinline__ void tile_coord(const GemmParams& p, int t, int& tm, 
 }
 __device__ __forceinline__ UnitCoord decode_unit(const GemmParams& p, int u) {
   UnitCoord c;
-  c.tail = -1;
-  if (p.rank_split) {
-    const int tiles = p.tiles_m * p.tiles_n;
-    c.step0 = u / tiles;
-    c.tile = u - c.step0 * tiles;
-    c.nsteps = 1;
-    c.split = 1;
-  } else if (u < p.main_tiles) {
+  c.kb0 = 0;
+  c.kb1 = p.k_blocks;
+  if (u < p.main_tiles) {
     c.step0 = 0;
     c.nsteps = p.steps_per_unit;
     c.split = 0;
     c.tile = u;
+    c.tail = -1;
+    c.weight = 0;
   } else {
-    const int v = u - p.main_tiles;
-    c.step0 = v / p.tail_tiles;
-    c.tail = v - c.step0 * p.tail_tiles;
+    int q = u - p.main_tiles;
+    c.weight = p.ksplit;
+    if (q >= p.full_units) {          // a K range of one of the last split_units product units
+      const int w = q - p.full_units;
+      const int part = w / p.split_units;
+      q = p.full_units + (w - part * p.split_units);
+      c.kb0 = (p.k_blocks * part) / p.ksplit;
+      c.kb1 = (p.k_blocks * (part + 1)) / p.ksplit;
+      c.weight = 1;
+    }
+    c.step0 = q / p.tail_tiles;
+    c.tail = q - c.step0 * p.tail_tiles;
     c.tile = p.main_tiles + c.tail;
     c.nsteps = 1;
     c.split = 1;
@@ -253,7 +269,7 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
                             static_cast<int>(cta_rank) * kBM;
           const int b_row = sd.b_plane * p.b_plane_rows + uc.tn * kBN +
                             static_cast<int>(cta_rank) * T::kBRows;
-          for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          for (int kb = uc.kb0; kb < uc.kb1; ++kb, ++it) {
             const uint32_t stage = it % T::kStages;
             const uint32_t phase = (it / T::kStages) & 1u;
             mbar_wait(empty_bar(stage), phase ^ 1u, ctl, kCodeProducer);
@@ -287,7 +303,7 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
           tcgen05_fence_after();
           const uint32_t d_tmem = tmem_base + as * kBN;
           const uint32_t keep = (uc.split || p.steps[s].clear) ? 0u : 1u;
-          for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          for (int kb = uc.kb0; kb < uc.kb1; ++kb, ++it) {
             const uint32_t stage = it % T::kStages;
             const uint32_t phase = (it / T::kStages) & 1u;
             mbar_wait(full_bar(stage), phase, ctl, kCodeMmaFull);
@@ -298,7 +314,7 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
             for (int k = 0; k < kBK / kUmmaK; ++k) {
               // +32 bytes per K=16 slice inside the 128-byte swizzle row
               umma_bf16<kCtaGroup>(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc,
-                                   (kb | k) != 0 ? 1u : keep);
+                                   (kb != uc.kb0 || k != 0) ? 1u : keep);
             }
             umma_commit<kCtaGroup>(empty_bar(stage));   // frees the stage in every CTA of the group
           }
@@ -391,8 +407,8 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
           if (uc.tail >= 0) {
             int* cnt = &g_tail_counters[p.chain.sched_slot][uc.tail * 2 + static_cast<int>(cta_rank)];
             __threadfence();
-            const int seen = atomicAdd(cnt, 1);
-            if (seen == p.chain.plane_steps_total - 1) {
+            const int seen = atomicAdd(cnt, uc.weight);
+            if (seen + uc.weight == p.chain.plane_steps_total) {
               __threadfence();
               *cnt = 0;
             } else {
@@ -686,6 +702,53 @@ int r7_geometry(int64_t M, int64_t N, int64_t K, R7Geometry* g) {
   return LCG_OK;
 }
 
+// The unit list of a launch (see GemmParams) for `tiles` tiles on `groups` CTA groups.
+void plan_units(int rank, int tiles, int groups, int k_blocks, int schedule, GemmParams* p) {
+  p->main_tiles = tiles;
+  p->tail_tiles = 0;
+  p->ksplit = 1;
+  p->zero_tail = 0;
+  if (schedule == LCG_SCHEDULE_RANK_SPLIT) {
+    p->main_tiles = 0;
+    p->tail_tiles = tiles;
+  } else if (schedule == LCG_SCHEDULE_HYBRID) {
+    // Whole waves walk all products per tile; the last partial wave is split by product when
+    // that shortens it: ceil(rank * tail / groups) single steps against `rank` steps.
+    const int tail = tiles % groups;
+    const int split_steps = (rank * tail + groups - 1) / groups;
+    if (tail > 0 && split_steps <= rank - 2 && 2 * tail <= kSchedSlotInts) {
+      p->main_tiles = tiles - tail;
+      p->tail_tiles = tail;
+      p->zero_tail = 1;
+    }
+  }
+  // Single-product units fill whole rounds of the CTA groups over the full K; the units of the
+  // last partial round are cut into `ksplit` K ranges so that the round shortens to
+  // ceil(rest * ksplit / groups) / ksplit of a unit (each extra range costs an epilogue).
+  const int prod_units = rank * p->tail_tiles;
+  p->full_units = prod_units;
+  p->split_units = 0;
+  const int rest = prod_units % groups;
+  if (rest > 0) {
+    int best_f = 1;
+    double best = 1.0;
+    for (int f = 2; f <= 8; ++f) {
+      if (k_blocks / f < 8) break;
+      const double cost = static_cast<double>((rest * f + groups - 1) / groups) / f + 0.02 * f;
+      if (cost < best - 0.05) {
+        best = cost;
+        best_f = f;
+      }
+    }
+    if (best_f > 1) {
+      p->ksplit = best_f;
+      p->full_units = prod_units - rest;
+      p->split_units = rest;
+    }
+  }
+  p->num_units = p->main_tiles + p->full_units + p->split_units * p->ksplit;
+}
+
 int fill_r7(const lcg_scheme* scheme, const void* a_planes, int64_t ld_a, const void* b_planes,
             int64_t ld_b, void* c, int64_t ldc, int64_t M, int64_t N, const R7Geometry& g,
             int schedule, int cta_group, CUtensorMap* ma, CUtensorMap* mb, CMaps* mc,
@@ -709,7 +772,6 @@ int fill_r7(const lcg_scheme* scheme, const void* a_planes, int64_t ld_a, const 
     p->steps_split[t] = scheme->rank_split[t];
   }
   p->steps_per_unit = scheme->rank;
-  p->rank_split = split ? 1 : 0;
   const int tiles_m_all = static_cast<int>((g.m2 + tile_m - 1) / tile_m);
   if (tm_end < 0) tm_end = tiles_m_all;
   if (tm_begin < 0 || tm_begin >= tm_end || tm_end > tiles_m_all)
@@ -721,21 +783,9 @@ int fill_r7(const lcg_scheme* scheme, const void* a_planes, int64_t ld_a, const 
   if (max_groups > 0 && max_groups < groups) groups = max_groups;
   p->max_groups = max_groups;
   p->group_m = pick_group_m(p->tiles_m, groups);
-  const int tiles = p->tiles_m * p->tiles_n;
-  p->main_tiles = tiles;
-  p->tail_tiles = 0;
-  if (schedule == LCG_SCHEDULE_HYBRID) {
-    // Whole waves walk all products per tile; the last partial wave is split by product when
-    // that shortens it: ceil(rank * tail / groups) single steps against `rank` steps.
-    const int tail = tiles % groups;
-    const int split_steps = (scheme->rank * tail + groups - 1) / groups;
-    if (tail > 0 && split_steps <= scheme->rank - 2 && 2 * tail <= kSchedSlotInts) {
-      p->main_tiles = tiles - tail;
-      p->tail_tiles = tail;
-    }
-  }
-  p->num_units = split ? tiles * scheme->rank : p->main_tiles + scheme->rank * p->tail_tiles;
   p->k_blocks = static_cast<int>(g.k2p / kBK);
+  plan_units(scheme->rank, p->tiles_m * p->tiles_n, groups, p->k_blocks, schedule, p);
+  p->num_units = p->main_tiles + p->full_units + p->split_units * p->ksplit;
   p->a_plane_rows = static_cast<int>(g.m2);
   p->b_plane_rows = static_cast<int>(g.n2);
   return LCG_OK;
@@ -744,7 +794,7 @@ int fill_r7(const lcg_scheme* scheme, const void* a_planes, int64_t ld_a, const 
 // The C blocks of the tail tiles receive reduce-adds only: clear them first, on the stream.
 int zero_tail_tiles(const GemmParams& p, void* c, int64_t ldc, int64_t M, int64_t N,
                     const R7Geometry& g, int cta_group, cudaStream_t stream) {
-  if (p.tail_tiles == 0) return LCG_OK;
+  if (p.tail_tiles == 0 || !p.zero_tail) return LCG_OK;
   ZeroArgs z;
   z.c = static_cast<__nv_bfloat16*>(c);
   z.ldc = ldc;
@@ -904,7 +954,7 @@ extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t*
   ch.m2 = static_cast<int32_t>(g.m2);
   ch.inter = static_cast<int32_t>(inter);
   ch.plane_rank = plane_scheme->rank;
-  ch.plane_steps_total = scheme->rank;
+  ch.plane_steps_total = scheme->rank * p.ksplit;
   ch.sched_slot = next_sched_slot();
   for (int r = 0; r < plane_scheme->rank; ++r)
     for (int x = 0; x < 4; ++x) ch.plane_terms.coef[r][x] = plane_scheme->a[r][x];
@@ -923,23 +973,20 @@ extern "C" int lcg_describe_gemm(int64_t M, int64_t N, int64_t K, int rank7, int
   const int stages = cta_group == 1 ? Tile<1>::kStages : Tile<2>::kStages;
   const int smem = cta_group == 1 ? Tile<1>::kSmemBytes : Tile<2>::kSmemBytes;
   int64_t rows = M, cols = N, kk = K;
-  int units_mul = 1;
   if (rank7) {
     R7Geometry g;
     if (int e = r7_geometry(M, N, K, &g)) return e;
     rows = g.m2;
     cols = g.n2;
     kk = g.k2p;
-    if (schedule == LCG_SCHEDULE_RANK_SPLIT) units_mul = 7;
   }
   const int64_t tm = (rows + tile_m - 1) / tile_m, tn = (cols + kBN - 1) / kBN;
   const int groups = sm_count() / cta_group;
-  int64_t units = tm * tn * units_mul;
-  if (rank7 && schedule == LCG_SCHEDULE_HYBRID) {
-    const int64_t tail = (tm * tn) % groups;
-    if (tail > 0 && (7 * tail + groups - 1) / groups <= 5 && 2 * tail <= kSchedSlotInts)
-      units = tm * tn - tail + 7 * tail;
-  }
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.num_units = static_cast<int>(tm * tn);
+  if (rank7) plan_units(7, static_cast<int>(tm * tn), groups, static_cast<int>((kk + kBK - 1) / kBK), schedule, &p);
+  const int64_t units = p.num_units;
   return snprintf(buf, buflen,
                   "%s %lldx%lldx%lld: tile %dx%dx%d cta_group=%d stages=%d smem=%dB tmem=512 cols (2 acc "
                   "stages); %lldx%lld tiles, %lld units over %d CTA groups (%.2f waves), %lld k-blocks/step",
