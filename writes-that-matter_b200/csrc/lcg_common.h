@@ -44,8 +44,10 @@ struct StepDesc {
 
 // Signed-sum tables for the SIMT plane producers: per rank, coefficient of
 // each of the four blocks (row-major over the 2x2 block grid).
+// Stored as floats: an int-to-float conversion per use would go through the SM's quarter-rate
+// conversion pipe, which is what these HBM-bound kernels run out of first.
 struct TermTable {
-  int8_t coef[kMaxRank][4];
+  float coef[kMaxRank][4];
 };
 
 }  // namespace lcg

@@ -501,9 +501,8 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
                 for (int e = 0; e < 8; ++e) o[e] = 0.f;
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
-                  const int cf = ch.plane_terms.coef[r][x];
-                  if (cf == 0) continue;
-                  const float w = static_cast<float>(cf);
+                  const float w = ch.plane_terms.coef[r][x];
+                  if (w == 0.f) continue;
 #pragma unroll
                   for (int e = 0; e < 8; ++e) o[e] = fmaf(w, sv[x][e], o[e]);
                 }
@@ -957,7 +956,7 @@ extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t*
   ch.plane_steps_total = scheme->rank * p.ksplit;
   ch.sched_slot = next_sched_slot();
   for (int r = 0; r < plane_scheme->rank; ++r)
-    for (int x = 0; x < 4; ++x) ch.plane_terms.coef[r][x] = plane_scheme->a[r][x];
+    for (int x = 0; x < 4; ++x) ch.plane_terms.coef[r][x] = static_cast<float>(plane_scheme->a[r][x]);
   ch.preclear = preclear_bytes > 0 ? static_cast<uint4*>(preclear) : nullptr;
   ch.preclear_vecs = preclear_bytes / 16;
   auto st_ = static_cast<cudaStream_t>(stream);

@@ -14,12 +14,13 @@ struct alignas(16) Vec8 {
   __nv_bfloat162 v[4];
 };
 
+// bf16 -> fp32 is a 16-bit shift: done with integer ops so that it stays off the conversion pipe.
 __device__ __forceinline__ void unpack8(const Vec8& p, float (&f)[8]) {
 #pragma unroll
   for (int t = 0; t < 4; ++t) {
-    const float2 x = __bfloat1622float2(p.v[t]);
-    f[2 * t] = x.x;
-    f[2 * t + 1] = x.y;
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(&p.v[t]);
+    f[2 * t] = __uint_as_float(w << 16);
+    f[2 * t + 1] = __uint_as_float(w & 0xffff0000u);
   }
 }
 
@@ -55,7 +56,10 @@ __device__ __forceinline__ void load8_guarded(const __nv_bfloat16* __restrict__ 
     return;
   }
 #pragma unroll
-  for (int t = 0; t < 8; ++t) f[t] = (col + t < col_limit) ? __bfloat162float(p[t]) : 0.f;
+  for (int t = 0; t < 8; ++t)
+    f[t] = (col + t < col_limit)
+               ? __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(p + t)) << 16)
+               : 0.f;
 }
 
 __device__ __forceinline__ void signed_sum(const TermTable& tt, int r, const float (&blk)[4][8],
@@ -66,9 +70,8 @@ __device__ __forceinline__ void signed_sum(const TermTable& tt, int r, const flo
   for (int t = 0; t < 8; ++t) out[t] = 0.f;
 #pragma unroll
   for (int x = 0; x < 4; ++x) {
-    const int cf = tt.coef[r][x];
-    if (cf == 0) continue;
-    const float w = static_cast<float>(cf);
+    const float w = tt.coef[r][x];
+    if (w == 0.f) continue;
 #pragma unroll
     for (int t = 0; t < 8; ++t) out[t] = fmaf(w, blk[x][t], out[t]);
   }
@@ -195,6 +198,100 @@ k_norm_planes(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __re
   }
 }
 
+// The same seam with the row pair staged in shared memory by cp.async: the loads of a CTA are
+// in flight without holding registers, more CTAs fit per SM, and the rounded sum h overwrites the
+// delta slot so that the second phase reads it back from shared memory.  Each thread only ever
+// touches the vectors it copied itself.  Used when the four rows (2 rows x delta, residual) fit:
+// 8 * K bytes of dynamic shared memory.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+
+__global__ void __launch_bounds__(512)
+k_norm_planes_staged(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __restrict__ residual,
+                     const __nv_bfloat16* __restrict__ norm_w, int m2, int k, float eps, int rank,
+                     TermTable tt, __nv_bfloat16* residual_out, __nv_bfloat16* __restrict__ out,
+                     int ld_out) {
+  extern __shared__ __align__(16) unsigned char stage_raw[];
+  __shared__ float s_part[2][16];
+  Vec8* stage = reinterpret_cast<Vec8*>(stage_raw);      // [(i * 2 + kb) * 2 + operand][nvec]
+  const int rho = blockIdx.x;
+  const int k2 = k / 2;
+  const int nvec = k2 / 8;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+
+  for (int v = tid; v < nvec; v += blockDim.x)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) {
+        const size_t off = (static_cast<size_t>(i) * m2 + rho) * k + kb * k2 + v * 8;
+        cp_async16(&stage[((i * 2 + kb) * 2 + 0) * nvec + v], delta + off);
+        cp_async16(&stage[((i * 2 + kb) * 2 + 1) * nvec + v], residual + off);
+      }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+  float ss[2] = {0.f, 0.f};
+  for (int v = tid; v < nvec; v += blockDim.x)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) {
+        float d[8], r[8], s[8];
+        unpack8(stage[((i * 2 + kb) * 2 + 0) * nvec + v], d);
+        unpack8(stage[((i * 2 + kb) * 2 + 1) * nvec + v], r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s[e] = d[e] + r[e];
+        const Vec8 h = pack8(s);          // the norm sees exactly what is stored as the residual
+        const size_t off = (static_cast<size_t>(i) * m2 + rho) * k + kb * k2 + v * 8;
+        *reinterpret_cast<Vec8*>(residual_out + off) = h;
+        stage[((i * 2 + kb) * 2 + 0) * nvec + v] = h;
+        float hf[8];
+        unpack8(h, hf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss[i] = fmaf(hf[e], hf[e], ss[i]);
+      }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], o);
+    if (lane == 0) s_part[i][warp] = ss[i];
+  }
+  __syncthreads();
+  float rstd[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float part = lane < nwarps ? s_part[i][lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    rstd[i] = rsqrtf(part / static_cast<float>(k) + eps);
+  }
+
+  for (int v = tid; v < nvec; v += blockDim.x) {
+    float y[4][8];
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+      float w[8];
+      unpack8(*reinterpret_cast<const Vec8*>(norm_w + kb * k2 + v * 8), w);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        float hf[8];
+        unpack8(stage[((i * 2 + kb) * 2 + 0) * nvec + v], hf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[i * 2 + kb][e] = hf[e] * rstd[i] * (w[e] + 1.0f);
+      }
+    }
+    for (int r = 0; r < rank; ++r) {
+      float o[8];
+      signed_sum(tt, r, y, o);
+      *reinterpret_cast<Vec8*>(out + (static_cast<size_t>(r) * m2 + rho) * ld_out + v * 8) = pack8(o);
+    }
+  }
+}
+
 // --------------------------------------------------------- SwiGLU + planes
 __device__ __forceinline__ float silu_f32(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
@@ -305,13 +402,13 @@ k_add(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
 TermTable a_table(const lcg_scheme* s) {
   TermTable t{};
   for (int r = 0; r < s->rank; ++r)
-    for (int x = 0; x < 4; ++x) t.coef[r][x] = s->a[r][x];
+    for (int x = 0; x < 4; ++x) t.coef[r][x] = static_cast<float>(s->a[r][x]);
   return t;
 }
 TermTable b_table(const lcg_scheme* s) {
   TermTable t{};
   for (int r = 0; r < s->rank; ++r)
-    for (int x = 0; x < 4; ++x) t.coef[r][x] = s->b[r][x];
+    for (int x = 0; x < 4; ++x) t.coef[r][x] = static_cast<float>(s->b[r][x]);
   return t;
 }
 
@@ -373,6 +470,28 @@ extern "C" int lcg_norm_planes(const lcg_scheme_t* scheme, const void* delta, co
     return fail(LCG_ERR_BAD_ARG, "plane leading dimension %lld must be >= %lld and a multiple of 8",
                 (long long)ld_out, (long long)k2p);
   const int64_t nvec_p = k2p / 8;
+  // Staged form: whole row pair in shared memory, when it fits three CTAs to an SM.
+  if (k2p == K / 2 && 8 * K <= 72 * 1024 && M / 2 <= 0x7fffffff && ld_out <= 0x7fffffff) {
+    const int nvec = static_cast<int>(K / 16);
+    const int threads = nvec >= 512 ? 512 : (nvec + 31) / 32 * 32;
+    const size_t smem = static_cast<size_t>(8) * K;
+    static bool configured[64] = {};
+    int dev = 0;
+    LCG_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+      LCG_CUDA_OK(cudaFuncSetAttribute(k_norm_planes_staged, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       72 * 1024));
+      if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    k_norm_planes_staged<<<static_cast<unsigned>(M / 2), threads, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(residual),
+        static_cast<const __nv_bfloat16*>(norm_weight), static_cast<int>(M / 2), static_cast<int>(K), eps,
+        scheme->rank, a_table(scheme), static_cast<__nv_bfloat16*>(residual_out),
+        static_cast<__nv_bfloat16*>(out), static_cast<int>(ld_out));
+    LCG_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return LCG_OK;
+  }
   int vpt = 1;
   while ((nvec_p + vpt - 1) / vpt > 1024) vpt *= 2;
   if (vpt > 4) return fail(LCG_ERR_UNSUPPORTED_SHAPE, "K=%lld too wide for the fused norm", (long long)K);
