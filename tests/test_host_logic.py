@@ -40,7 +40,7 @@ def test_patch_state_machine_errors():
             with pytest.raises(RuntimeError, match="arm"):
                 patch.install(object(), tokens=4096)
         if not patch._STATE["installed"]:
-            with pytest.raises(RuntimeError, match="before install"):
+            with pytest.raises(RuntimeError, match="needs install"):
                 patch.check_calls(1)
         assert isinstance(patch.counts(), dict)
 

@@ -1,7 +1,8 @@
-"""Which exact batch-one prefill sizes deploy the rank-7 chain (``lcgemm/qwen_policy.py``).
+"""Engine selection for exact batch-one Qwen prefill lengths.
 
-Stock sizes must use a process in which the decoder patch was never armed; rank-7 sizes
-use one engine per exact prefill length.
+The reference's policy (``lcgemm/qwen_policy.py``): 512 and 1024 tokens deploy the stock engine
+-- in a process where the decoder patch was never armed -- and 2048 / 4096 / 8192 deploy the
+rank-7 chain, one engine per exact length; anything else has no validated policy.
 """
 from __future__ import annotations
 
@@ -10,44 +11,48 @@ from typing import Literal
 
 Deployment = Literal["stock", "lc_chain"]
 
-STOCK_TOKENS = frozenset((512, 1024))
-LC_TOKENS = frozenset((2048, 4096, 8192))
-SUPPORTED_TOKENS = STOCK_TOKENS | LC_TOKENS
+_POLICY: dict = {512: "stock", 1024: "stock", 2048: "lc_chain", 4096: "lc_chain", 8192: "lc_chain"}
+STOCK_TOKENS = frozenset(t for t, kind in _POLICY.items() if kind == "stock")
+LC_TOKENS = frozenset(t for t, kind in _POLICY.items() if kind == "lc_chain")
+SUPPORTED_TOKENS = frozenset(_POLICY)
+_PATCH_MODULE = "lcgemm.integrate.qwen_patch"
 
 
 def deployment_for(tokens: int) -> Deployment:
-    """The validated engine kind for an exact batch-one prefill size."""
-    if tokens in STOCK_TOKENS:
-        return "stock"
-    if tokens in LC_TOKENS:
-        return "lc_chain"
-    raise ValueError(
-        f"no validated Qwen engine policy for M={tokens}; supported={sorted(SUPPORTED_TOKENS)}")
+    """Which engine kind a prefill of exactly ``tokens`` tokens deploys."""
+    try:
+        return _POLICY[tokens]
+    except (KeyError, TypeError):
+        known = ", ".join(str(t) for t in sorted(SUPPORTED_TOKENS))
+        raise ValueError(f"prefill length {tokens!r} has no Qwen engine policy (known: {known})") from None
 
 
 def arm_selected_engine(tokens: int):
-    """Arm the rank-7 engine before vLLM is imported, or leave a stock engine truly unarmed.
-    Returns the patch module to hand to :func:`install_selected_engine`, or ``None`` for stock
-    (in which case the patch module is deliberately not imported)."""
-    if deployment_for(tokens) == "stock":
-        loaded = sys.modules.get("lcgemm.integrate.qwen_patch")
-        if loaded is not None and getattr(loaded, "_STATE", {}).get("armed"):
-            raise RuntimeError(
-                "cannot construct a truly unarmed stock engine after the Qwen decoder patch was "
-                "armed in this process; use a fresh process")
-        return None
-    if "vllm" in sys.modules:
-        raise RuntimeError("select and arm the LC engine before importing vLLM")
-    from lcgemm.integrate import qwen_patch
+    """Prepare the process for the engine ``tokens`` deploys.
 
-    qwen_patch.arm()
-    return qwen_patch
+    Rank-7 lengths: import and arm the patch (this must happen before vLLM is imported) and
+    return the patch module for :func:`install_selected_engine`.  Stock lengths: return ``None``
+    without importing the patch at all, and refuse if it was already armed in this process."""
+    kind = deployment_for(tokens)
+    if kind == "lc_chain":
+        if "vllm" in sys.modules:
+            raise RuntimeError("vLLM is already imported: the rank-7 engine has to be armed first")
+        from lcgemm.integrate import qwen_patch
+
+        qwen_patch.arm()
+        return qwen_patch
+    patch = sys.modules.get(_PATCH_MODULE)
+    if patch is not None and getattr(patch, "_STATE", {}).get("armed"):
+        raise RuntimeError(
+            "this process has armed the Qwen decoder patch, so no stock engine built here would "
+            "be unpatched; start the stock engine in a fresh process")
+    return None
 
 
 def install_selected_engine(patch, llm, tokens: int):
-    """Install exactly one validated rank-7 shape after the engine has loaded its weights."""
+    """After the engine has loaded its weights: install the one validated rank-7 shape."""
     if deployment_for(tokens) != "lc_chain":
-        raise ValueError(f"M={tokens} is a stock-only policy; do not arm or install the patch")
+        raise ValueError(f"{tokens} tokens deploy the stock engine: nothing to install")
     if patch is None:
-        raise ValueError("the LC patch returned by arm_selected_engine is required")
+        raise ValueError("pass the module arm_selected_engine() returned")
     return patch.install(llm, tokens=tokens)
