@@ -67,6 +67,31 @@ def _(delta, residual, norm_weight, gate_up_weight, down_weight, eps):
     return delta.new_empty((delta.shape[0], down_weight.shape[0])), torch.empty_like(delta)
 
 
+_ATTENTION_TAKES_OUTPUT: dict = {}
+
+
+def _attention(module, hidden_states, positions=None):
+    """Call an attention module under either calling convention vLLM has used for this layer:
+    returning its result (the revision the reference pins, ``qwen_patch.py:134-148`` there) or
+    filling a caller-allocated ``output`` buffer (the installed 0.22 series)."""
+    cls = type(module)
+    takes_output = _ATTENTION_TAKES_OUTPUT.get(cls)
+    if takes_output is None:
+        import inspect
+
+        names = inspect.signature(module.forward).parameters
+        takes_output = _ATTENTION_TAKES_OUTPUT[cls] = ("output" in names, "positions" in names)
+    wants_output, wants_positions = takes_output
+    kwargs = {"hidden_states": hidden_states}
+    if wants_positions and positions is not None:
+        kwargs["positions"] = positions
+    if wants_output:
+        out = torch.empty_like(hidden_states)
+        module(output=out, **kwargs)
+        return out
+    return module(**kwargs)
+
+
 def _plus_one_scale(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     s = scale.to(x.dtype)
     return x * ((s[0] if x.dim() == 2 else s) + 1)
@@ -75,7 +100,7 @@ def _plus_one_scale(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
 def _patched_forward(self, hidden_states, residual, positions=None, **kwargs):
     """The decoder layer with its MLP half replaced by the custom op; the attention half is the
     model's own (``lcgemm/integrate/qwen_patch.py:116-178``)."""
-    if self.use_attn_reduce_scatter_for_moe:          # sequence-parallel MoE path: not this campaign
+    if getattr(self, "use_attn_reduce_scatter_for_moe", False):   # sequence-parallel MoE path: stock
         return _ORIGINAL_FORWARD(self, hidden_states=hidden_states, residual=residual,
                                  positions=positions, **kwargs)
     if residual is None:
@@ -84,9 +109,9 @@ def _patched_forward(self, hidden_states, residual, positions=None, **kwargs):
         hidden_states, residual = self.input_layernorm(hidden_states, residual)
 
     if self.layer_type == "full_attention":
-        hidden_states = self.self_attn(hidden_states=hidden_states, positions=positions)
+        hidden_states = _attention(self.self_attn, hidden_states, positions)
     elif self.layer_type == "linear_attention":
-        hidden_states = self.linear_attn(hidden_states=hidden_states)
+        hidden_states = _attention(self.linear_attn, hidden_states)
     else:
         raise ValueError(f"invalid Qwen layer type {self.layer_type}")
     if self.layer_scale:
