@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Metric (BASELINE.json): MLP prefill effective TFLOP/s (6*M*H*I / time for one layer:
+Metric: MLP prefill effective TFLOP/s (6*M*H*I / time for one layer:
 gate_up + down, dense-equivalent FLOPs) and % speedup over the dense bf16 path.
 
 N = 1   one "step" = one fused MLP layer of the single-layer configuration
@@ -119,7 +119,7 @@ class ClockWatch:
 
 # ------------------------------------------------------------------ synthetic data
 def make_layer_tensors(tokens, hidden, inter, device, seed=0, inter_local=None, rank=0):
-    """Seeded synthetic tensors with the distributions BASELINE.json names: x ~ N(0,1),
+    """Seeded synthetic tensors with the benchmark's distributions: x ~ N(0,1),
     norm weight stored as w with effective scale 1 + w, w ~ N(0, 0.01), weights ~ N(0, 0.02)."""
     g = torch.Generator(device=device).manual_seed(seed)
     bf = torch.bfloat16
@@ -230,8 +230,8 @@ def run_reference_arm(args, rank):
 
 def _workload_name(gpus):
     if gpus == 1:
-        return "single fused MLP layer, 4096 tokens x 5120, intermediate 17408 (BASELINE config 2)"
-    return f"tensor-parallel MLP tp={gpus}, 8192 tokens x 8192, intermediate 28672 (BASELINE config 4)"
+        return "single fused MLP layer, 4096 tokens x 5120, intermediate 17408 (the single-layer configuration)"
+    return f"tensor-parallel MLP tp={gpus}, 8192 tokens x 8192, intermediate 28672 (the tensor-parallel configuration)"
 
 
 # --------------------------------------------------------------------- our arm
@@ -491,7 +491,7 @@ def run_case(args, device):
 
 
 def run_sweep(args, device):
-    """BASELINE config 5: bare rank-7 GEMM (A planes + GEMM, B planes prepared offline) against
+    """The bare-GEMM sweep: rank-7 GEMM (A planes + GEMM, B planes prepared offline) against
     the dense tcgen05 GEMM and cuBLAS, odd shapes included, one JSON line per shape."""
     from lcgemm import ops, scheme as S
 
@@ -537,7 +537,7 @@ def run_sweep(args, device):
 
 
 def run_model(args, device):
-    """BASELINE config 3: batch-1 prefill of a random-init 64-layer dense decoder, stock MLP vs
+    """The end-to-end configuration: batch-1 prefill of a random-init 64-layer dense decoder, stock MLP vs
     rank-7 MLP, on seeded uniform-random prompts of 2048 / 4096 / 8192 tokens."""
     from lcgemm import ops
     from lcgemm.model import DecoderConfig, RandomInitDecoder, compare_arms
@@ -578,12 +578,12 @@ def run_model(args, device):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", action="store_true",
-                    help="end-to-end prefill of the random-init decoder (BASELINE config 3)")
+                    help="end-to-end prefill of the random-init decoder")
     ap.add_argument("--layers", type=int, default=64, help="decoder layers for --model")
     ap.add_argument("--case", default=None,
                     help="time one kernel alone: gate_up | down | norm_planes | a_planes | dense_gate_up")
     ap.add_argument("--tokens", type=int, default=4096, help="token count for --case")
-    ap.add_argument("--sweep", action="store_true", help="bare-GEMM shape sweep (BASELINE config 5)")
+    ap.add_argument("--sweep", action="store_true", help="bare-GEMM shape sweep, odd shapes included")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)

@@ -192,7 +192,7 @@ int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_sche
  *
  * Who needs it: hosts that give all free device memory to their own pool at start-up
  * (an inference server sizing its KV cache from what is left), so that a plugin's
- * later cudaMalloc fails or eats into that budget, and serving paths on which
+ * later cudaMalloc fails or eats into that pool, and serving paths on which
  * allocation is forbidden because cudaMalloc synchronises the device.
  *
  * The A planes -- the scratch lcg_a_planes + lcg_gemm_r7 keep in a caller-owned buffer

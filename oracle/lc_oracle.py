@@ -249,7 +249,7 @@ def combine_as_kernel(prods, tb: Tables, m: int, n: int, rank_split: bool = Fals
 def scheme_matmul(a: torch.Tensor, w: torch.Tensor, tb: Tables, mode: str = "fp32") -> torch.Tensor:
     """C = A @ W^T through the scheme.  ``w`` is (N, K) as the reference stores weights.
 
-    mode "fp32":   planes, products and combine in the input precision (BASELINE config 1);
+    mode "fp32":   planes, products and combine in the input precision (the fp32 CPU configuration);
     mode "planes": bf16 planes (one rounding each), fp32 products and combine;
     mode "kernel": bf16 planes and the kernels' publication rounding, all-ranks schedule;
     mode "kernel_split": the same with the rank-split schedule."""

@@ -13,7 +13,7 @@ the reference's own host functions on seeded CPU inputs and writes
     mlp_reference.npz    the functional MLP reference and the Muse RMSNorm helper
     evaluator.npz        the scheme evaluator composed from the reference's pieces
                          (A planes by the chain_a_planes pattern, prepare_b, products,
-                         C combine over c_terms), fp32, BASELINE config-1 distribution
+                         C combine over c_terms), fp32, A ~ N(0,1), B ~ N(0,0.02)
 
 bf16 tensors are stored as their int16 bit patterns.
 """
