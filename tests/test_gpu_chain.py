@@ -29,7 +29,7 @@ def _layer_inputs(m, h, i, seed=0):
             seeded((2 * i, h), seed + 4, 0.02), seeded((h, i), seed + 5, 0.02))
 
 
-@pytest.mark.parametrize("dims", [(256, 256, 512), (512, 384, 1280), (130, 128, 256)])
+@pytest.mark.parametrize("dims", [(256, 256, 512), (512, 384, 1280), (130, 128, 256), (258, 128, 384), (2, 128, 128)])
 def test_chain_against_oracle(lc, dims):
     m, h, i = dims
     delta, residual, nw, wgu, wd = _layer_inputs(m, h, i)

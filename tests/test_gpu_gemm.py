@@ -73,6 +73,27 @@ def test_rank7_gemm_against_oracle(lc, name, group, schedule, shape):
     assert rel_fro(c, model) <= (TOL_R7_ORACLE_SPLIT if schedule else TOL_R7_ORACLE)
 
 
+@pytest.mark.parametrize("shape", [(2, 16, 2), (3, 17, 5), (7, 9, 130), (129, 257, 66)])
+def test_rank7_tiny_and_ragged_shapes(lc, shape):
+    m, n, k = shape
+    sch = lc.load("2x2_locality_ordered")
+    a, w = seeded((m, k), 11), seeded((n, k), 12, 0.5)
+    for schedule in (0, 1, 2):
+        c = lc.ops.gemm_r7(a, lc.planes.prepare_b(w, sch), n, sch, schedule=schedule)
+        assert c.shape == (m, n)
+        want = a.double().cpu() @ w.double().cpu().T
+        assert rel_fro(c, want) <= 1.5e-2
+
+
+def test_rank7_rejects_degenerate_shapes(lc):
+    sch = lc.load("2x2_locality_ordered")
+    a, w = seeded((4, 16), 1), seeded((8, 16), 2)
+    with pytest.raises(ValueError):                        # N = 8 leaves the second column block empty
+        lc.ops.gemm_r7(a, lc.planes.prepare_b(w, sch), 8, sch)
+    with pytest.raises(ValueError):
+        lc.ops.gemm_dense(a, seeded((8, 24), 3))           # inner dimensions differ
+
+
 def test_rank7_odd_shape_pad_path(lc):
     """K=5000, N=13999 (scaled down in M): planes are zero-padded, C blocks are clipped."""
     m, n, k = 257, 13999, 5000
