@@ -37,11 +37,33 @@ constexpr int kEpiCols = 64;    // columns per staged epilogue sub-tile
 constexpr int kEpiBytes = kBM * kEpiCols * 2;
 constexpr int kEpiBufs = 2;
 constexpr uint32_t kTmemCols = 512;
-constexpr int kEpiWarp0 = 2;
-constexpr int kPlaneWarp0 = 6;
 constexpr int kPlaneThreads = 256;
 constexpr int kThreadsPlain = 192;
-constexpr int kThreadsChain = 192 + kPlaneThreads;
+constexpr int kThreadsChain = 512;
+
+// Which warp plays which part.  A warp issues from scheduler (warp % 4) of the SM, and an
+// epilogue warp reads the TMEM lane quarter (warp % 4), so one epilogue warp sits on every
+// scheduler whatever the layout.  The two single-thread warps that drive the operand ring (TMA
+// producer, MMA issuer) are on its critical loop: every cycle one of their instructions waits
+// for an issue slot is a cycle added to the stage-recycle round trip.  In the chained kernel the
+// eight plane warps are busy SIMT code, so they stay off the scheduler those two live on:
+//   plain   (6 warps):  0 producer, 1 MMA, 2-5 epilogue
+//   chained (16 warps): 0 producer, 4 MMA (both scheduler 0), 1 2 3 8 epilogue,
+//                       5 6 7 9 10 11 13 14 plane warps (schedulers 1-3), 12 15 idle
+template <bool kChain>
+struct Roles {
+  static constexpr int kProducer = 0;
+  static constexpr int kMma = kChain ? 4 : 1;
+  static constexpr int kEpiIssuer = kChain ? 1 : 2;
+  __device__ static bool is_epilogue(int warp) {
+    return kChain ? (warp == 1 || warp == 2 || warp == 3 || warp == 8) : (warp >= 2 && warp < 6);
+  }
+  // index 0..7 of a plane warp, or -1
+  __device__ static int plane_index(int warp) {
+    if (!kChain || (warp & 3) == 0 || warp < 5 || warp > 14) return -1;
+    return warp < 8 ? warp - 5 : (warp < 12 ? warp - 6 : warp - 7);
+  }
+};
 
 // Codes left in the status word by a wait that ran out.
 constexpr int kCodeProducer = 101, kCodeMmaAcc = 102, kCodeMmaFull = 103, kCodeEpilogue = 104,
@@ -244,7 +266,8 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
     prefetch_tensormap(&tma_b);
     prefetch_tensormap(&tma_c.m[0]);
   }
-  if (warp == 1) {
+  using R = Roles<kChain>;
+  if (warp == R::kMma) {
     tmem_alloc<kCtaGroup>(misc, kTmemCols);
     tmem_relinquish<kCtaGroup>();
   }
@@ -257,7 +280,8 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
   tcgen05_fence_after();
   const uint32_t tmem_base = misc_gen[0];
 
-  if (warp == 0) {
+  const int plane_warp = R::plane_index(warp);
+  if (warp == R::kProducer) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
@@ -289,7 +313,7 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == R::kMma) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0 && leader) {
       constexpr uint32_t idesc = make_idesc_bf16(kBM * kCtaGroup, kBN);
@@ -323,11 +347,11 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
       }
     }
     __syncwarp();
-  } else if (warp < kPlaneWarp0) {
+  } else if (R::is_epilogue(warp)) {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;                 // TMEM lanes this warp may touch
     const int row = quarter * 32 + lane;          // row inside the CTA's 128-row tile
-    const bool issuer = warp == kEpiWarp0 && lane == 0;
+    const bool issuer = warp == R::kEpiIssuer && lane == 0;
     const uint32_t acc_empty_remote =
         kCtaGroup == 2 ? mapa_shared(acc_empty_bar(0), 0) : acc_empty_bar(0);
     uint32_t acc_it = 0, epi_it = 0, units_done = 0;
@@ -427,11 +451,12 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
     if (issuer) bulk_wait_group<0>();
     __syncwarp();
   } else if constexpr (kChain) {
+    if (plane_warp >= 0) {
     // ------------------------------------------------------------- plane warps
     // 256 threads; 16 slots across (chunk pair, 8-column vector), 16 rows per pass, two
     // passes (16 x 16-byte loads per thread) in flight at a time.
     const ChainParams& ch = p.chain;
-    const int ptid = threadIdx.x - kPlaneWarp0 * 32;
+    const int ptid = plane_warp * 32 + lane;
     const int slot = ptid & 15;
     const int pair = slot >> 3;
     const int vc = slot & 7;
@@ -524,11 +549,12 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
       if (ptid == 0) st_release_shared(plane_done_addr, seq + 1);
     }
     for (int t = static_cast<int>(seq); t < ch.iters_max; ++t) clear_share(t);
+    }   // plane warps (the two spare warps of the block go straight to the teardown)
   }
 
   // ------------------------------------------------------------------ teardown
   __syncwarp();
-  if (misc_gen[1] != 0u && warp == 0) {
+  if (misc_gen[1] != 0u && warp == R::kProducer) {
     // A wait ran out somewhere: loads may still be in flight towards this CTA's
     // shared memory.  Give them time to land before the CTA goes away.
     const uint64_t t0 = globaltimer_ns();
@@ -540,7 +566,7 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
     cluster_arrive();
     cluster_wait();
   }
-  if (warp == 1) {
+  if (warp == R::kMma) {
     tcgen05_fence_after();
     tmem_dealloc<kCtaGroup>(tmem_base, kTmemCols);
   }
@@ -765,7 +791,6 @@ int fill_r7(const lcg_scheme* scheme, const void* a_planes, int64_t ld_a, const 
       if (int e = make_map(&mc->m[bi * 2 + bj], blk, cols, rows, ldc, kBM, "C block")) return e;
     }
   std::memset(p, 0, sizeof(*p));
-  const bool split = schedule == LCG_SCHEDULE_RANK_SPLIT;
   for (int t = 0; t < scheme->rank; ++t) {
     p->steps[t] = scheme->all_ranks[t];
     p->steps_split[t] = scheme->rank_split[t];
