@@ -283,8 +283,12 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
   const int plane_warp = R::plane_index(warp);
   if (warp == R::kProducer) {
     // ------------------------------------------------------------ TMA producer
+    // The loop body is kept to the few instructions it needs (running stage, parity and K
+    // coordinate; addresses hoisted): this thread's latency is part of the stage-recycle loop.
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t stage = 0, wait_parity = 1;   // parity of the "empty" phase to wait for
+      // Both CTAs of a pair post their bytes on the leader's barriers.
+      const uint32_t full_remote0 = kCtaGroup == 2 ? mapa_shared(full_bar(0), 0) : full_bar(0);
       for (int u = group_id; u < p.num_units; u += num_groups) {
         const UnitCoord uc = decode_unit(p, u);
         for (int s = uc.step0; s < uc.step0 + uc.nsteps; ++s) {
@@ -293,20 +297,23 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
                             static_cast<int>(cta_rank) * kBM;
           const int b_row = sd.b_plane * p.b_plane_rows + uc.tn * kBN +
                             static_cast<int>(cta_rank) * T::kBRows;
-          for (int kb = uc.kb0; kb < uc.kb1; ++kb, ++it) {
-            const uint32_t stage = it % T::kStages;
-            const uint32_t phase = (it / T::kStages) & 1u;
-            mbar_wait(empty_bar(stage), phase ^ 1u, ctl, kCodeProducer);
+          int kcol = uc.kb0 * kBK;
+          for (int kb = uc.kb0; kb < uc.kb1; ++kb, kcol += kBK) {
+            mbar_wait(empty_bar(stage), wait_parity, ctl, kCodeProducer);
+            const uint32_t sa = a_smem(stage);
             if constexpr (kCtaGroup == 1) {
               mbar_arrive_expect_tx(full_bar(stage), T::kStageBytes);
-              tma_load_2d(a_smem(stage), &tma_a, full_bar(stage), kb * kBK, a_row);
-              tma_load_2d(b_smem(stage), &tma_b, full_bar(stage), kb * kBK, b_row);
+              tma_load_2d(sa, &tma_a, full_bar(stage), kcol, a_row);
+              tma_load_2d(sa + T::kABytes, &tma_b, full_bar(stage), kcol, b_row);
             } else {
-              // Both CTAs of the pair post their bytes on the leader's barrier.
               if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * T::kStageBytes);
-              const uint32_t bar = mapa_shared(full_bar(stage), 0);
-              tma_load_2d_pair(a_smem(stage), &tma_a, bar, kb * kBK, a_row);
-              tma_load_2d_pair(b_smem(stage), &tma_b, bar, kb * kBK, b_row);
+              const uint32_t bar = full_remote0 + 8u * stage;
+              tma_load_2d_pair(sa, &tma_a, bar, kcol, a_row);
+              tma_load_2d_pair(sa + T::kABytes, &tma_b, bar, kcol, b_row);
+            }
+            if (++stage == T::kStages) {
+              stage = 0;
+              wait_parity ^= 1u;
             }
           }
         }
@@ -317,7 +324,11 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0 && leader) {
       constexpr uint32_t idesc = make_idesc_bf16(kBM * kCtaGroup, kBN);
-      uint32_t it = 0, acc_it = 0;
+      uint32_t stage = 0, parity = 0, acc_it = 0;
+      // Operand descriptors of stage 0; a stage further on adds its byte offset >> 4 to the
+      // address field (stages are 1024-byte aligned, so nothing carries out of the field).
+      const uint64_t adesc0 = make_kmajor_sw128_desc(a_smem(0));
+      const uint64_t bdesc0 = make_kmajor_sw128_desc(b_smem(0));
       for (int u = group_id; u < p.num_units; u += num_groups) {
         const UnitCoord uc = decode_unit(p, u);
         for (int s = uc.step0; s < uc.step0 + uc.nsteps; ++s, ++acc_it) {
@@ -326,21 +337,24 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
           mbar_wait(acc_empty_bar(as), aphase ^ 1u, ctl, kCodeMmaAcc);
           tcgen05_fence_after();
           const uint32_t d_tmem = tmem_base + as * kBN;
-          const uint32_t keep = (uc.split || p.steps[s].clear) ? 0u : 1u;
-          for (int kb = uc.kb0; kb < uc.kb1; ++kb, ++it) {
-            const uint32_t stage = it % T::kStages;
-            const uint32_t phase = (it / T::kStages) & 1u;
-            mbar_wait(full_bar(stage), phase, ctl, kCodeMmaFull);
+          uint32_t accumulate = (uc.split || p.steps[s].clear) ? 0u : 1u;
+          for (int kb = uc.kb0; kb < uc.kb1; ++kb) {
+            mbar_wait(full_bar(stage), parity, ctl, kCodeMmaFull);
             tcgen05_fence_after();
-            const uint64_t adesc = make_kmajor_sw128_desc(a_smem(stage));
-            const uint64_t bdesc = make_kmajor_sw128_desc(b_smem(stage));
+            const uint64_t soff = static_cast<uint64_t>(stage * (T::kStageBytes >> 4));
+            const uint64_t adesc = adesc0 + soff;
+            const uint64_t bdesc = bdesc0 + soff;
+            // +32 bytes per K=16 slice inside the 128-byte swizzle row
+            umma_bf16<kCtaGroup>(d_tmem, adesc, bdesc, idesc, accumulate);
 #pragma unroll
-            for (int k = 0; k < kBK / kUmmaK; ++k) {
-              // +32 bytes per K=16 slice inside the 128-byte swizzle row
-              umma_bf16<kCtaGroup>(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc,
-                                   (kb != uc.kb0 || k != 0) ? 1u : keep);
-            }
+            for (int k = 1; k < kBK / kUmmaK; ++k)
+              umma_bf16<kCtaGroup>(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, 1u);
+            accumulate = 1u;
             umma_commit<kCtaGroup>(empty_bar(stage));   // frees the stage in every CTA of the group
+            if (++stage == T::kStages) {
+              stage = 0;
+              parity ^= 1u;
+            }
           }
           umma_commit<kCtaGroup>(acc_full_bar(as));
         }
