@@ -177,8 +177,9 @@ int lcg_gemm_r7_slab(const lcg_scheme_t* scheme, const void* a_planes, int64_t l
  * optionally zeroes `preclear` (preclear_bytes, multiple of 16) for a
  * rank-split consumer (lcgemm/kernels/sm100.py:779-815).
  * `schedule` is LCG_SCHEDULE_ALL_RANKS or LCG_SCHEDULE_HYBRID; with the hybrid schedule the
- * tail tiles' seven products come from different CTAs and the one that lands last runs the
- * tile's SwiGLU/plane phase (completion counters live in the library and are left clean).
+ * tail tiles' seven products come from different CTAs, so their SwiGLU/plane phase runs in a
+ * small second kernel queued behind the GEMM on the same stream (the library keeps no state
+ * between launches).
  * Needs M % 2 == 0, N % 256 == 0, K % 128 == 0. */
 int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_scheme,
                       const void* a_planes, int64_t ld_a, const void* b_planes, int64_t ld_b,
@@ -232,11 +233,6 @@ int lcg_swiglu(const void* z, int64_t M, int64_t I, int64_t ldz, void* s, int64_
 int lcg_add(const void* a, const void* b, void* out, int64_t n, void* stream);
 
 /* ---- introspection ------------------------------------------------------- */
-
-/* Clear the library's tail-tile completion counters on the current device.  Only needed
- * after a launch reported a device-side timeout in its status word (the counters of that
- * launch may be left mid-count); asynchronous on `stream`. */
-int lcg_reset_state(void* stream);
 
 /* Kernel launches issued by this library in this process (for the bench's
  * `gpu_launches`). */

@@ -104,9 +104,11 @@ def test_full_size_chain_qwen_4096(lc):
     mlp_r7 = out[::3].float() - x[::3].float()
     mlp_cb = cb[::3].float() - x[::3].float()
     assert rel_fro(mlp_r7, mlp_cb) <= 5e-2
-    # a second pass over the same buffers gives the same answer (pre-clear works every time)
+    # a second pass over the same buffers gives the same answer (pre-clear works every time) up to
+    # the order of the rank-split down projection's bf16 reduce-adds, which differs run to run
+    # (most on a cold first launch): same 8e-3 as rank-split against the ordered schedule
     out2 = r7(x)
-    assert rel_fro(out2, out) < 4e-3
+    assert rel_fro(out2, out) < 8e-3
 
 
 def test_layer_arms_small_against_reference(lc):

@@ -85,13 +85,6 @@ struct CMaps {
   CUtensorMap m[4];
 };
 
-// Completion counters of the tail tiles of a chained hybrid launch: one per (tail tile, CTA of
-// the pair).  A launch takes one slot of the pool in turn; the CTA that records the last of a
-// tile's seven products resets the counter, so a slot is clean again when its launch ends.
-constexpr int kSchedSlots = 64;
-constexpr int kSchedSlotInts = 256;
-__device__ int g_tail_counters[kSchedSlots][kSchedSlotInts];
-
 struct ChainParams {
   const __nv_bfloat16* z;     // the GEMM's own output, re-read L2-hot
   int64_t ldz;
@@ -101,8 +94,6 @@ struct ChainParams {
   int32_t inter;              // I: S columns; gate block = z[:, :I], up block = z[:, I:]
   int32_t plane_rank;
   int32_t iters_max;          // most work units any CTA group walks
-  int32_t sched_slot;         // which row of g_tail_counters this launch uses
-  int32_t plane_steps_total;  // weight that completes a tail tile: products per tile * ksplit
   TermTable plane_terms;
   uint4* preclear;            // consumer output to zero, or null
   int64_t preclear_vecs;
@@ -143,7 +134,6 @@ struct UnitCoord {
   int tile;            // linear tile index
   int tail;            // index among the tail tiles, or -1
   int kb0, kb1;        // K blocks [kb0, kb1) of every step of the unit
-  int weight;          // arrivals this unit counts for in its tail tile's completion counter
   int tm, tn;
 };
 __device__ __forceinline__ void tile_coord(const GemmParams& p, int t, int& tm, int& tn) {
@@ -164,17 +154,14 @@ __device__ __forceinline__ UnitCoord decode_unit(const GemmParams& p, int u) {
     c.split = 0;
     c.tile = u;
     c.tail = -1;
-    c.weight = 0;
   } else {
     int q = u - p.main_tiles;
-    c.weight = p.ksplit;
     if (q >= p.full_units) {          // a K range of one of the last split_units product units
       const int w = q - p.full_units;
       const int part = w / p.split_units;
       q = p.full_units + (w - part * p.split_units);
       c.kb0 = (p.k_blocks * part) / p.ksplit;
       c.kb1 = (p.k_blocks * (part + 1)) / p.ksplit;
-      c.weight = 1;
     }
     c.step0 = q / p.tail_tiles;
     c.tail = q - c.step0 * p.tail_tiles;
@@ -213,6 +200,71 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& q, float (&f)[8]) {
 // silu(g) = g / (1 + e^-g) with the fast exponential and reciprocal (2 ulp each); large |g| is safe:
 // e^-g -> inf gives -0, e^-g -> 0 gives g.
 __device__ __forceinline__ float silu_dev(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+
+// SwiGLU and the consumer's A planes for 32 rows of one tile column: rows [row0, row0 + 32) of
+// each block row of Z, S columns [tn * 256, tn * 256 + 256) of the gate and the up block, read
+// L2-hot; plane columns [tn * 128, +128).  256 threads: 16 slots across (chunk pair, 8-column
+// vector), 16 rows per pass, two passes (16 x 16-byte loads per thread) in flight at a time.
+__device__ __forceinline__ void plane_rows32(const ChainParams& ch, int tn, int row0, int ptid) {
+  const int slot = ptid & 15;
+  const int pair = slot >> 3;
+  const int vc = slot & 7;
+  const int rsub = ptid >> 4;
+  const int scol = tn * kBN + pair * 128 + vc * 8;     // S column of chunk h = 0
+  const int pcol = tn * (kBN / 2) + pair * 64 + vc * 8;
+  if (scol + 64 >= ch.inter) return;
+  uint4 q[2][2][2][2];
+  int rho[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    rho[t] = row0 + rsub + t * 16;
+    if (rho[t] < ch.m2) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh)
+            q[t][i][j][hh] = __ldcg(reinterpret_cast<const uint4*>(
+                ch.z + (static_cast<int64_t>(i) * ch.m2 + rho[t]) * ch.ldz +
+                static_cast<int64_t>(j) * ch.inter + scol + hh * 64));
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    if (rho[t] >= ch.m2) continue;
+    float sv[4][8];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        float g[8], uu[8];
+        unpack_bf16x8(q[t][i][0][hh], g);
+        unpack_bf16x8(q[t][i][1][hh], uu);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sv[i * 2 + hh][e] = silu_dev(g[e]) * uu[e];
+      }
+    for (int r = 0; r < ch.plane_rank; ++r) {
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = 0.f;
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const float w = ch.plane_terms.coef[r][x];
+        if (w == 0.f) continue;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = fmaf(w, sv[x][e], o[e]);
+      }
+      uint4 outv;
+      outv.x = pack_bf16x2(o[0], o[1]);
+      outv.y = pack_bf16x2(o[2], o[3]);
+      outv.z = pack_bf16x2(o[4], o[5]);
+      outv.w = pack_bf16x2(o[6], o[7]);
+      *reinterpret_cast<uint4*>(ch.planes + (static_cast<int64_t>(r) * ch.m2 + rho[t]) * ch.ld_planes +
+                                pcol) = outv;
+    }
+  }
+}
 
 template <int kCtaGroup, bool kChain>
 __global__ void __launch_bounds__(kChain ? kThreadsChain : kThreadsPlain, 1)
@@ -435,23 +487,15 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
       }
       if constexpr (kChain) {
         // Hand the unit to the plane warps.  A whole tile's C blocks are final once this CTA's
-        // bulk copies have landed (single writer).  A tail tile is final when the last of its
-        // seven products has landed, whichever CTA that is: each records its arrival in the
-        // tile's counter and the one that completes the count takes the plane job.
+        // bulk copies have landed (single writer), so its plane job runs here, under the next
+        // tile's MMAs.  A tail tile is written by several CTAs and is final only when the kernel
+        // ends: its planes are formed by k_tail_planes, launched behind this kernel.
         if (issuer) {
-          bulk_wait_group<0>();
-          fence_proxy_async_all();
-          int job = uc.tile;
-          if (uc.tail >= 0) {
-            int* cnt = &g_tail_counters[p.chain.sched_slot][uc.tail * 2 + static_cast<int>(cta_rank)];
-            __threadfence();
-            const int seen = atomicAdd(cnt, uc.weight);
-            if (seen + uc.weight == p.chain.plane_steps_total) {
-              __threadfence();
-              *cnt = 0;
-            } else {
-              job = -1;
-            }
+          int job = -1;
+          if (uc.tail < 0) {
+            bulk_wait_group<0>();
+            fence_proxy_async_all();
+            job = uc.tile;
           }
           // the ring entry being overwritten must have been consumed
           if (units_done >= kJobRing - 1)
@@ -467,14 +511,8 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
   } else if constexpr (kChain) {
     if (plane_warp >= 0) {
     // ------------------------------------------------------------- plane warps
-    // 256 threads; 16 slots across (chunk pair, 8-column vector), 16 rows per pass, two
-    // passes (16 x 16-byte loads per thread) in flight at a time.
     const ChainParams& ch = p.chain;
     const int ptid = plane_warp * 32 + lane;
-    const int slot = ptid & 15;
-    const int pair = slot >> 3;
-    const int vc = slot & 7;
-    const int rsub = ptid >> 4;
     const int tiles_total = p.tiles_m * p.tiles_n;
     const int64_t clear_stride =
         static_cast<int64_t>(gridDim.x) * kPlaneThreads * ch.iters_max;
@@ -498,65 +536,8 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
         int tm, tn;
         tile_coord(p, job, tm, tn);
         const int row_base = tm * T::kTileM + static_cast<int>(cta_rank) * kBM;
-        const int scol = tn * kBN + pair * 128 + vc * 8;     // S column of chunk h = 0
-        const int pcol = tn * (kBN / 2) + pair * 64 + vc * 8;
-        if (scol + 64 < ch.inter) {
 #pragma unroll 1
-          for (int step = 0; step < kBM / 32; ++step) {
-            uint4 q[2][2][2][2];
-            int rho[2];
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-              rho[t] = row_base + rsub + (2 * step + t) * 16;
-              if (rho[t] < ch.m2) {
-#pragma unroll
-                for (int i = 0; i < 2; ++i)
-#pragma unroll
-                  for (int j = 0; j < 2; ++j)
-#pragma unroll
-                    for (int hh = 0; hh < 2; ++hh)
-                      q[t][i][j][hh] = __ldcg(reinterpret_cast<const uint4*>(
-                          ch.z + (static_cast<int64_t>(i) * ch.m2 + rho[t]) * ch.ldz +
-                          static_cast<int64_t>(j) * ch.inter + scol + hh * 64));
-              }
-            }
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-              if (rho[t] >= ch.m2) continue;
-              float sv[4][8];
-#pragma unroll
-              for (int i = 0; i < 2; ++i)
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                  float g[8], uu[8];
-                  unpack_bf16x8(q[t][i][0][hh], g);
-                  unpack_bf16x8(q[t][i][1][hh], uu);
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) sv[i * 2 + hh][e] = silu_dev(g[e]) * uu[e];
-                }
-              for (int r = 0; r < ch.plane_rank; ++r) {
-                float o[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = 0.f;
-#pragma unroll
-                for (int x = 0; x < 4; ++x) {
-                  const float w = ch.plane_terms.coef[r][x];
-                  if (w == 0.f) continue;
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) o[e] = fmaf(w, sv[x][e], o[e]);
-                }
-                uint4 outv;
-                outv.x = pack_bf16x2(o[0], o[1]);
-                outv.y = pack_bf16x2(o[2], o[3]);
-                outv.z = pack_bf16x2(o[4], o[5]);
-                outv.w = pack_bf16x2(o[6], o[7]);
-                *reinterpret_cast<uint4*>(ch.planes +
-                                          (static_cast<int64_t>(r) * ch.m2 + rho[t]) * ch.ld_planes +
-                                          pcol) = outv;
-              }
-            }
-          }
-        }
+        for (int step = 0; step < kBM / 32; ++step) plane_rows32(ch, tn, row_base + step * 32, ptid);
       }
       // every plane thread has read its ring entry: the epilogue may reuse it
       named_bar_sync(2, kPlaneThreads);
@@ -612,6 +593,19 @@ k_zero_tail_tiles(const __grid_constant__ GemmParams p, const ZeroArgs z) {
       for (int e = 0; col + e < c1; ++e) ptr[e] = __float2bfloat16(0.f);
     }
   }
+}
+
+// SwiGLU + consumer planes of the tail tiles of a chained hybrid launch, behind the GEMM kernel
+// (their C blocks are sums over several CTAs and final only when it ends).  One CTA per 32 rows
+// of a tile: grid = tail tiles * tile_m / 32, 256 threads.
+__global__ void __launch_bounds__(kPlaneThreads)
+k_tail_planes(const __grid_constant__ GemmParams p, const int tile_m) {
+  const int chunks = tile_m / 32;
+  const int n = static_cast<int>(blockIdx.x) / chunks;
+  const int c = static_cast<int>(blockIdx.x) - n * chunks;
+  int tm, tn;
+  tile_coord(p, p.main_tiles + n, tm, tn);
+  plane_rows32(p.chain, tn, tm * tile_m + c * 32, static_cast<int>(threadIdx.x));
 }
 
 // ============================================================== host side
@@ -755,7 +749,7 @@ void plan_units(int rank, int tiles, int groups, int k_blocks, int schedule, Gem
     // that shortens it: ceil(rank * tail / groups) single steps against `rank` steps.
     const int tail = tiles % groups;
     const int split_steps = (rank * tail + groups - 1) / groups;
-    if (tail > 0 && split_steps <= rank - 2 && 2 * tail <= kSchedSlotInts) {
+    if (tail > 0 && split_steps <= rank - 2) {
       p->main_tiles = tiles - tail;
       p->tail_tiles = tail;
       p->zero_tail = 1;
@@ -845,11 +839,6 @@ int zero_tail_tiles(const GemmParams& p, void* c, int64_t ldc, int64_t M, int64_
   LCG_CUDA_OK(cudaGetLastError());
   count_launch();
   return LCG_OK;
-}
-
-int next_sched_slot() {
-  static std::atomic<unsigned> turn{0};
-  return static_cast<int>(turn.fetch_add(1, std::memory_order_relaxed) % kSchedSlots);
 }
 
 }  // namespace
@@ -992,15 +981,21 @@ extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t*
   ch.m2 = static_cast<int32_t>(g.m2);
   ch.inter = static_cast<int32_t>(inter);
   ch.plane_rank = plane_scheme->rank;
-  ch.plane_steps_total = scheme->rank * p.ksplit;
-  ch.sched_slot = next_sched_slot();
   for (int r = 0; r < plane_scheme->rank; ++r)
     for (int x = 0; x < 4; ++x) ch.plane_terms.coef[r][x] = static_cast<float>(plane_scheme->a[r][x]);
   ch.preclear = preclear_bytes > 0 ? static_cast<uint4*>(preclear) : nullptr;
   ch.preclear_vecs = preclear_bytes / 16;
   auto st_ = static_cast<cudaStream_t>(stream);
   if (int e = zero_tail_tiles(p, z, ldz, M, N, g, cta_group, st_)) return e;
-  return cta_group == 1 ? launch<1, true>(ma, mb, mc, p, st_) : launch<2, true>(ma, mb, mc, p, st_);
+  if (int e = cta_group == 1 ? launch<1, true>(ma, mb, mc, p, st_) : launch<2, true>(ma, mb, mc, p, st_))
+    return e;
+  if (p.tail_tiles > 0) {
+    const int tile_m = kBM * cta_group;
+    k_tail_planes<<<p.tail_tiles * (tile_m / 32), kPlaneThreads, 0, st_>>>(p, tile_m);
+    LCG_CUDA_OK(cudaGetLastError());
+    count_launch();
+  }
+  return LCG_OK;
 }
 
 extern "C" int lcg_describe_gemm(int64_t M, int64_t N, int64_t K, int rank7, int schedule,
@@ -1034,14 +1029,6 @@ extern "C" int lcg_describe_gemm(int64_t M, int64_t N, int64_t K, int rank7, int
                   (long long)M, (long long)K, (long long)N, tile_m, kBN, kBK, cta_group, stages, smem,
                   (long long)tm, (long long)tn, (long long)units, groups,
                   static_cast<double>(units) / groups, (long long)((kk + kBK - 1) / kBK));
-}
-
-extern "C" int lcg_reset_state(void* stream) {
-  void* ptr = nullptr;
-  LCG_CUDA_OK(cudaGetSymbolAddress(&ptr, g_tail_counters));
-  LCG_CUDA_OK(cudaMemsetAsync(ptr, 0, sizeof(int) * kSchedSlots * kSchedSlotInts,
-                              static_cast<cudaStream_t>(stream)));
-  return LCG_OK;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -46,7 +46,6 @@ SIGNATURES = {
                                 _i32, _i32, _i32, _vp, _vp]),
     "lcg_gate_up_chain": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
                                  _vp, _i64, _vp, _i64, _i32, _i32, _vp, _vp]),
-    "lcg_reset_state": (_i32, [_vp]),
     "lcg_selftest_wait_timeout": (_i32, [_vp, _i64, _vp, _vp]),
     "lcg_gemm_r7_static": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _i32,
                                   _vp, _vp]),

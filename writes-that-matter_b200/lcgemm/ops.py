@@ -43,7 +43,6 @@ def check_status(device=None) -> None:
     code = int(word[0].item())
     if code != 0:
         word.zero_()
-        lib().lcg_reset_state(stream_ptr())
         raise RuntimeError(
             f"lcgemm_b200: a device-side wait ran out (code {code}: 101 producer, 102/103 MMA "
             f"issuer, 104 epilogue, 105 plane warps); results of that launch are invalid")
