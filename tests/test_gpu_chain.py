@@ -71,8 +71,8 @@ def test_fused_epilogue_equals_unfused_kernels(lc, group, dims):
     assert bool((pc == 0).all())
     # Hybrid schedule: the tail tiles' products arrive as reduce-adds from several CTAs, so Z
     # agrees within the rank-split tolerance; the planes must still be exactly the transform
-    # of the Z this launch produced (the last arrival runs the plane phase of a tail tile).
-    for _ in range(2):                                      # twice: counters are left clean
+    # of the Z this launch produced (the tail tiles' plane phase runs behind the GEMM kernel).
+    for _ in range(2):                                      # twice: no state is carried over
         z2 = torch.full_like(z, 5.0)
         pl2 = torch.full_like(pl, 3.0)
         pc.fill_(1.0)
