@@ -188,6 +188,42 @@ int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_sche
                       void* preclear, int64_t preclear_bytes, int schedule, int cta_group,
                       int32_t* status, void* stream);
 
+/* ---- tensor parallel over peer memory (NVLink / NVSwitch) ------------------
+ * The reference runs on one GPU (lcgemm/integrate/qwen_patch.py:216-217 refuses TP > 1);
+ * the three entry points below have no counterpart there.  One process per GPU; the caller
+ * exchanges device pointers of peer-mapped buffers (CUDA IPC or symmetric memory) once.
+ *
+ * lcg_gemm_r7_push: the row-parallel `down` projection of one rank.  Rank-7 C = A @ B^T from
+ * prepared planes into this rank's partial `c` (M, N) with the hybrid schedule, and, in the
+ * same kernel, one tile behind the mainloop, every finished tile is copied to the rank that
+ * owns its rows: row g belongs to rank g / rows_per_owner and lands in slots[owner], an
+ * (rows_per_owner, N) row-major region of the owner's memory reserved for this rank
+ * (slots is a host array of `world` device pointers; slots[rank] is local).  The tail tiles
+ * of the hybrid schedule are pushed by a small second kernel behind the GEMM.  N % 8 == 0,
+ * c 16-byte aligned, ldc % 8 == 0, world <= 8. */
+int lcg_gemm_r7_push(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,
+                     const void* b_planes, int64_t ld_b, void* c, int64_t ldc,
+                     int64_t M, int64_t N, int64_t K, void* const* slots, int world, int rank,
+                     int64_t rows_per_owner, int cta_group, int32_t* status, void* stream);
+
+/* Barrier between the ranks, on the stream: flags is a host array of `world` device pointers,
+ * flags[r] = rank r's array of 8 uint32 words (zero before the first barrier), peer-mapped.
+ * Rank `rank` writes `epoch` into word `rank` of every rank's array and waits until its own
+ * array holds `epoch` or more in every word; epochs must grow from call to call.  The wait
+ * is bounded by limit_us: when it runs out the kernel writes 106 into `status` (may be NULL)
+ * and returns, and the context stays usable. */
+int lcg_peer_barrier(void* const* flags, int world, int rank, uint32_t epoch, int64_t limit_us,
+                     int32_t* status, void* stream);
+
+/* The other half of the exchange, one kernel per rank: for the rows this rank owns,
+ * out = bf16(h + sum over ranks of slots[w]) (fp32, ranks in index order), written into every
+ * rank's output buffer (outs: host array of `world` device pointers to contiguous (M, cols)
+ * buffers, peer-mapped).  slots: this rank's (world, rows_per_owner, cols) receive region;
+ * h: the local (M, cols) residual with leading dimension ld_h.  cols % 8 == 0. */
+int lcg_reduce_gather(const void* slots, const void* h, int64_t ld_h, void* const* outs,
+                      int64_t M, int64_t cols, int64_t rows_per_owner, int world, int rank,
+                      void* stream);
+
 /* Rank-7 C = A @ B^T straight from the activation matrix, for callers that cannot
  * allocate device memory.  This entry point has no counterpart in the reference.
  *

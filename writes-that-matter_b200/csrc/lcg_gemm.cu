@@ -99,6 +99,20 @@ struct ChainParams {
   int64_t preclear_vecs;
 };
 
+// Tensor-parallel push: where the rows of this rank's finished C tiles go.  Row g of the (M, N)
+// partial belongs to rank g / rows_per_owner; it is copied to slot[owner], an (rows_per_owner, N)
+// row-major region of the owner's memory reserved for this rank (a peer-mapped address, or a
+// local one for the rank's own rows), with plain 16-byte stores over NVLink.
+constexpr int kMaxWorld = 8;
+struct PushParams {
+  const __nv_bfloat16* c;
+  int64_t ldc;
+  __nv_bfloat16* slot[kMaxWorld];
+  int32_t world;              // 0: no push
+  int32_t rows_per_owner;
+  int32_t m, n, m2, n2;
+};
+
 struct GemmParams {
   StepDesc steps[kMaxRank];        // whole-tile walk: chain plan, store-first scatter (or the dense step)
   StepDesc steps_split[kMaxRank];  // one product alone, reduce-add only
@@ -122,6 +136,7 @@ struct GemmParams {
   int32_t a_plane_rows, b_plane_rows;
   int32_t* status;
   ChainParams chain;
+  PushParams push;
 };
 
 // Work unit -> (first step, tile row, tile column).  Tiles are walked in bands of
@@ -266,8 +281,47 @@ __device__ __forceinline__ void plane_rows32(const ChainParams& ch, int tn, int 
   }
 }
 
-template <int kCtaGroup, bool kChain>
-__global__ void __launch_bounds__(kChain ? kThreadsChain : kThreadsPlain, 1)
+// The push counterpart of plane_rows32: rows [row0, row0 + 32) of each block row, columns
+// [tn * 256, tn * 256 + 256) of each block column of this rank's C, read L2-hot and stored into
+// the owners' slots.  256 threads: 32 16-byte vectors across, 8 rows per pass; per block row the
+// 8 loads of a thread (4 passes x 2 block columns) are in flight together.
+__device__ __forceinline__ void push_rows32(const PushParams& pp, int tn, int row0, int ptid) {
+  const int col = tn * kBN + (ptid & 31) * 8;
+  const int rsub = ptid >> 5;
+  const bool col_ok[2] = {col + 8 <= pp.n2, col + 8 <= pp.n - pp.n2};
+#pragma unroll 1
+  for (int bi = 0; bi < 2; ++bi) {
+    const int rows = bi == 0 ? pp.m2 : pp.m - pp.m2;
+    uint4 q[4][2];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int r = row0 + rsub + 8 * t;
+#pragma unroll
+      for (int bj = 0; bj < 2; ++bj)
+        if (r < rows && col_ok[bj])
+          q[t][bj] = __ldcg(reinterpret_cast<const uint4*>(
+              pp.c + (static_cast<int64_t>(bi) * pp.m2 + r) * pp.ldc + bj * pp.n2 + col));
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int r = row0 + rsub + 8 * t;
+      if (r >= rows) continue;
+      const int grow = bi * pp.m2 + r;
+      const int owner = grow / pp.rows_per_owner;
+      const int lrow = grow - owner * pp.rows_per_owner;
+      __nv_bfloat16* dst = pp.slot[owner] + static_cast<int64_t>(lrow) * pp.n + col;
+#pragma unroll
+      for (int bj = 0; bj < 2; ++bj)
+        if (col_ok[bj]) __stcg(reinterpret_cast<uint4*>(dst + bj * pp.n2), q[t][bj]);
+    }
+  }
+}
+
+// kMode: 0 plain GEMM; 1 chained (plane warps form SwiGLU + the consumer's planes behind each
+// tile); 2 push (the same warps copy each finished tile to the rank that owns its rows).
+constexpr int kModePlain = 0, kModePlanes = 1, kModePush = 2;
+template <int kCtaGroup, int kMode>
+__global__ void __launch_bounds__(kMode != kModePlain ? kThreadsChain : kThreadsPlain, 1)
 k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
        const __grid_constant__ CMaps tma_c, const __grid_constant__ GemmParams p) {
   using T = Tile<kCtaGroup>;
@@ -318,6 +372,7 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
     prefetch_tensormap(&tma_b);
     prefetch_tensormap(&tma_c.m[0]);
   }
+  constexpr bool kChain = kMode != kModePlain;
   using R = Roles<kChain>;
   if (warp == R::kMma) {
     tmem_alloc<kCtaGroup>(misc, kTmemCols);
@@ -536,8 +591,13 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
         int tm, tn;
         tile_coord(p, job, tm, tn);
         const int row_base = tm * T::kTileM + static_cast<int>(cta_rank) * kBM;
+        if constexpr (kMode == kModePush) {
 #pragma unroll 1
-        for (int step = 0; step < kBM / 32; ++step) plane_rows32(ch, tn, row_base + step * 32, ptid);
+          for (int step = 0; step < kBM / 32; ++step) push_rows32(p.push, tn, row_base + step * 32, ptid);
+        } else {
+#pragma unroll 1
+          for (int step = 0; step < kBM / 32; ++step) plane_rows32(ch, tn, row_base + step * 32, ptid);
+        }
       }
       // every plane thread has read its ring entry: the epilogue may reuse it
       named_bar_sync(2, kPlaneThreads);
@@ -595,8 +655,9 @@ k_zero_tail_tiles(const __grid_constant__ GemmParams p, const ZeroArgs z) {
   }
 }
 
-// SwiGLU + consumer planes of the tail tiles of a chained hybrid launch, behind the GEMM kernel
-// (their C blocks are sums over several CTAs and final only when it ends).  One CTA per 32 rows
+// SwiGLU + consumer planes (or the tensor-parallel push) of the tail tiles of a chained hybrid
+// launch, behind the GEMM kernel (their C blocks are sums over several CTAs and final only when
+// it ends).  One CTA per 32 rows
 // of a tile: grid = tail tiles * tile_m / 32, 256 threads.
 __global__ void __launch_bounds__(kPlaneThreads)
 k_tail_planes(const __grid_constant__ GemmParams p, const int tile_m) {
@@ -605,7 +666,10 @@ k_tail_planes(const __grid_constant__ GemmParams p, const int tile_m) {
   const int c = static_cast<int>(blockIdx.x) - n * chunks;
   int tm, tn;
   tile_coord(p, p.main_tiles + n, tm, tn);
-  plane_rows32(p.chain, tn, tm * tile_m + c * 32, static_cast<int>(threadIdx.x));
+  if (p.push.world > 0)
+    push_rows32(p.push, tn, tm * tile_m + c * 32, static_cast<int>(threadIdx.x));
+  else
+    plane_rows32(p.chain, tn, tm * tile_m + c * 32, static_cast<int>(threadIdx.x));
 }
 
 // ============================================================== host side
@@ -680,11 +744,12 @@ int pick_group_m(int tiles_m, int groups) {
   return best;
 }
 
-template <int kCtaGroup, bool kChain>
+template <int kCtaGroup, int kMode>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CMaps& mc, GemmParams& p,
            cudaStream_t stream) {
   using T = Tile<kCtaGroup>;
-  auto kern = k_gemm<kCtaGroup, kChain>;
+  constexpr bool kChain = kMode != kModePlain;
+  auto kern = k_gemm<kCtaGroup, kMode>;
   static bool configured[64] = {};   // per device: the attribute belongs to the device's context
   int dev = 0;
   LCG_CUDA_OK(cudaGetDevice(&dev));
@@ -880,7 +945,7 @@ extern "C" int lcg_gemm_dense(const void* a, int64_t lda, const void* b, int64_t
   p.k_blocks = static_cast<int>((K + kBK - 1) / kBK);
   p.status = status;
   auto st_ = static_cast<cudaStream_t>(stream);
-  return cta_group == 1 ? launch<1, false>(ma, mb, mc, p, st_) : launch<2, false>(ma, mb, mc, p, st_);
+  return cta_group == 1 ? launch<1, kModePlain>(ma, mb, mc, p, st_) : launch<2, kModePlain>(ma, mb, mc, p, st_);
 }
 
 extern "C" int lcg_gemm_r7(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,
@@ -906,7 +971,7 @@ extern "C" int lcg_gemm_r7(const lcg_scheme_t* scheme, const void* a_planes, int
   p.status = status;
   auto st_ = static_cast<cudaStream_t>(stream);
   if (int e = zero_tail_tiles(p, c, ldc, M, N, g, cta_group, st_)) return e;
-  return cta_group == 1 ? launch<1, false>(ma, mb, mc, p, st_) : launch<2, false>(ma, mb, mc, p, st_);
+  return cta_group == 1 ? launch<1, kModePlain>(ma, mb, mc, p, st_) : launch<2, kModePlain>(ma, mb, mc, p, st_);
 }
 
 extern "C" int lcg_gemm_r7_slab(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,
@@ -933,7 +998,7 @@ extern "C" int lcg_gemm_r7_slab(const lcg_scheme_t* scheme, const void* a_planes
   p.status = status;
   auto st_ = static_cast<cudaStream_t>(stream);
   if (int e = zero_tail_tiles(p, c, ldc, M, N, g, cta_group, st_)) return e;
-  return cta_group == 1 ? launch<1, false>(ma, mb, mc, p, st_) : launch<2, false>(ma, mb, mc, p, st_);
+  return cta_group == 1 ? launch<1, kModePlain>(ma, mb, mc, p, st_) : launch<2, kModePlain>(ma, mb, mc, p, st_);
 }
 
 extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_scheme,
@@ -987,7 +1052,61 @@ extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t*
   ch.preclear_vecs = preclear_bytes / 16;
   auto st_ = static_cast<cudaStream_t>(stream);
   if (int e = zero_tail_tiles(p, z, ldz, M, N, g, cta_group, st_)) return e;
-  if (int e = cta_group == 1 ? launch<1, true>(ma, mb, mc, p, st_) : launch<2, true>(ma, mb, mc, p, st_))
+  if (int e = cta_group == 1 ? launch<1, kModePlanes>(ma, mb, mc, p, st_) : launch<2, kModePlanes>(ma, mb, mc, p, st_))
+    return e;
+  if (p.tail_tiles > 0) {
+    const int tile_m = kBM * cta_group;
+    k_tail_planes<<<p.tail_tiles * (tile_m / 32), kPlaneThreads, 0, st_>>>(p, tile_m);
+    LCG_CUDA_OK(cudaGetLastError());
+    count_launch();
+  }
+  return LCG_OK;
+}
+
+extern "C" int lcg_gemm_r7_push(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,
+                                const void* b_planes, int64_t ld_b, void* c, int64_t ldc, int64_t M,
+                                int64_t N, int64_t K, void* const* slots, int world, int rank,
+                                int64_t rows_per_owner, int cta_group, int32_t* status,
+                                void* stream) {
+  if (!scheme || !a_planes || !b_planes || !c || !slots) return fail(LCG_ERR_BAD_ARG, "NULL operand");
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world)
+    return fail(LCG_ERR_BAD_ARG, "world must be 1..%d and rank inside it; got world=%d rank=%d",
+                kMaxWorld, world, rank);
+  if (rows_per_owner < 1 || rows_per_owner * world < M)
+    return fail(LCG_ERR_BAD_ARG, "rows_per_owner * world must cover M");
+  if (N % 8 != 0) return fail(LCG_ERR_UNSUPPORTED_SHAPE, "the push moves 16-byte vectors: N %% 8 must be 0");
+  for (int w = 0; w < world; ++w) {
+    if (!slots[w]) return fail(LCG_ERR_BAD_ARG, "NULL slot pointer for owner %d", w);
+    if ((reinterpret_cast<uintptr_t>(slots[w]) & 15u) != 0)
+      return fail(LCG_ERR_MISALIGNED, "slot pointers must be 16-byte aligned");
+  }
+  cta_group = resolve_group(cta_group);
+  if (cta_group != 1 && cta_group != 2) return fail(LCG_ERR_BAD_ARG, "cta_group must be 0, 1 or 2");
+  R7Geometry g;
+  if (int e = r7_geometry(M, N, K, &g)) return e;
+  if (ldc < N || ldc % 8 != 0 || (reinterpret_cast<uintptr_t>(c) & 15u) != 0)
+    return fail(LCG_ERR_MISALIGNED, "C must be 16-byte aligned with ldc %% 8 == 0 and ldc >= N");
+  if (ld_a < g.k2p || ld_b < g.k2p) return fail(LCG_ERR_BAD_ARG, "plane leading dimension below K2p");
+  CUtensorMap ma, mb;
+  CMaps mc;
+  GemmParams p;
+  if (int e = fill_r7(scheme, a_planes, ld_a, b_planes, ld_b, c, ldc, M, N, g, LCG_SCHEDULE_HYBRID,
+                      cta_group, &ma, &mb, &mc, &p))
+    return e;
+  p.status = status;
+  PushParams& pp = p.push;
+  pp.c = static_cast<const __nv_bfloat16*>(c);
+  pp.ldc = ldc;
+  for (int w = 0; w < world; ++w) pp.slot[w] = static_cast<__nv_bfloat16*>(slots[w]);
+  pp.world = world;
+  pp.rows_per_owner = static_cast<int32_t>(rows_per_owner);
+  pp.m = static_cast<int32_t>(M);
+  pp.n = static_cast<int32_t>(N);
+  pp.m2 = static_cast<int32_t>(g.m2);
+  pp.n2 = static_cast<int32_t>(g.n2);
+  auto st_ = static_cast<cudaStream_t>(stream);
+  if (int e = zero_tail_tiles(p, c, ldc, M, N, g, cta_group, st_)) return e;
+  if (int e = cta_group == 1 ? launch<1, kModePush>(ma, mb, mc, p, st_) : launch<2, kModePush>(ma, mb, mc, p, st_))
     return e;
   if (p.tail_tiles > 0) {
     const int tile_m = kBM * cta_group;

@@ -16,7 +16,7 @@ CSRC = _PKG.parent / "csrc"
 INCLUDE = _PKG.parent.parent / "include"
 LIB_DIR = _PKG / "_lib"
 LIB_PATH = LIB_DIR / "liblcgemm_b200.so"
-SOURCES = ("lcg_scheme.cu", "lcg_simt.cu", "lcg_gemm.cu", "lcg_static.cu")
+SOURCES = ("lcg_scheme.cu", "lcg_simt.cu", "lcg_gemm.cu", "lcg_static.cu", "lcg_peer.cu")
 
 OK = 0
 ERR_BAD_ARG, ERR_UNSUPPORTED_SHAPE, ERR_MISALIGNED, ERR_SCHEME, ERR_CUDA, ERR_DEVICE_TIMEOUT = (
@@ -46,6 +46,10 @@ SIGNATURES = {
                                 _i32, _i32, _i32, _vp, _vp]),
     "lcg_gate_up_chain": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
                                  _vp, _i64, _vp, _i64, _i32, _i32, _vp, _vp]),
+    "lcg_gemm_r7_push": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _i32,
+                                _i64, _i32, _vp, _vp]),
+    "lcg_peer_barrier": (_i32, [_vp, _i32, _i32, _c.c_uint32, _i64, _vp, _vp]),
+    "lcg_reduce_gather": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "lcg_selftest_wait_timeout": (_i32, [_vp, _i64, _vp, _vp]),
     "lcg_gemm_r7_static": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _i32,
                                   _vp, _vp]),

@@ -45,7 +45,8 @@ def check_status(device=None) -> None:
         word.zero_()
         raise RuntimeError(
             f"lcgemm_b200: a device-side wait ran out (code {code}: 101 producer, 102/103 MMA "
-            f"issuer, 104 epilogue, 105 plane warps); results of that launch are invalid")
+            f"issuer, 104 epilogue, 105 plane warps, 106 barrier between ranks); results of that "
+            f"launch are invalid")
 
 
 def launch_count() -> int:
@@ -221,6 +222,42 @@ def gate_up_chain(scheme, plane_scheme, a_pl, b_pl, z, down_planes, preclear=Non
                                   z.stride(0), m, n, k, ptr(down_planes), down_planes.stride(0),
                                   pc_ptr, pc_bytes, schedule, cta_group, ptr(status_word(z.device)),
                                   stream_ptr()))
+
+
+# ------------------------------------------------- tensor parallel, peer memory
+def _ptr_table(ptrs):
+    return (ctypes.c_void_p * len(ptrs))(*[int(v) for v in ptrs])
+
+
+def gemm_r7_push(scheme, a_pl, b_pl, m: int, n: int, k: int, c: torch.Tensor, slot_ptrs, rank: int,
+                 rows_per_owner: int, cta_group: int = 0) -> None:
+    """Row-parallel rank-7 ``down`` of one rank: the partial into ``c`` and, from the same
+    kernel, every finished tile's rows into ``slot_ptrs[owner]`` (device addresses of this
+    rank's ``(rows_per_owner, n)`` region in each owner's memory)."""
+    _need(a_pl, "A planes"), _need(b_pl, "B planes"), _need(c, "c")
+    if tuple(c.shape) != (m, n):
+        raise ValueError(f"c must be ({m}, {n}), got {tuple(c.shape)}")
+    check(lib().lcg_gemm_r7_push(NativeScheme.of(scheme).handle, ptr(a_pl), a_pl.stride(0), ptr(b_pl),
+                                 b_pl.stride(0), ptr(c), c.stride(0), m, n, k, _ptr_table(slot_ptrs),
+                                 len(slot_ptrs), rank, rows_per_owner, cta_group,
+                                 ptr(status_word(c.device)), stream_ptr()))
+
+
+def peer_barrier(flag_ptrs, rank: int, epoch: int, limit_us: int = 10_000_000, device=None) -> None:
+    """Barrier between the ranks on the current stream (bounded wait; code 106 on run-out)."""
+    check(lib().lcg_peer_barrier(_ptr_table(flag_ptrs), len(flag_ptrs), rank, epoch & 0xFFFFFFFF,
+                                 limit_us, ptr(status_word(device)), stream_ptr()))
+
+
+def reduce_gather(slots: torch.Tensor, h: torch.Tensor, out_ptrs, rows_per_owner: int, rank: int) -> None:
+    """``out[rows of rank] = bf16(h + sum_w slots[w])`` stored into every rank's output."""
+    _need(slots, "slots"), _need(h, "h")
+    world, rpo, cols = slots.shape
+    if rpo != rows_per_owner or world != len(out_ptrs) or not slots.is_contiguous():
+        raise ValueError("slots must be a contiguous (world, rows_per_owner, cols) tensor")
+    m = h.shape[0]
+    check(lib().lcg_reduce_gather(ptr(slots), ptr(h), h.stride(0), _ptr_table(out_ptrs), m, cols,
+                                  rows_per_owner, world, rank, stream_ptr()))
 
 
 # -------------------------------------------------------------- dense seams

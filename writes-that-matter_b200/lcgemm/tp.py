@@ -18,6 +18,15 @@ the all-reduce of each finished slab (two row ranges, one per block row) runs as
 while the next slab computes; the GEMM then leaves ``reserve_groups`` CTA pairs' worth of SMs
 free, because one of its CTAs fills an SM's shared memory and NCCL's kernels could not start
 beside it.
+
+With ``fused=True`` the exchange runs in this package's own kernels over peer memory instead of
+the library all-reduce.  Row ``g`` of the output belongs to rank ``g // ceil(M / tp)``.  Each
+rank's ``down`` GEMM copies every finished tile, from inside the GEMM kernel, into the owner's
+receive region over NVLink (the reduce-scatter half, hidden under the GEMM); after a barrier
+each owner sums the ``tp`` partials and the residual in fp32 and stores the finished rows into
+every rank's output (the all-gather half), and a second barrier closes the layer.  The buffers
+are ``torch.distributed._symmetric_memory`` allocations; the receive regions are double-buffered
+so that a fast rank's next layer cannot overwrite what a slow owner is still reading.
 """
 from __future__ import annotations
 
@@ -46,6 +55,57 @@ def all_reduce_sum(t: torch.Tensor, group=None) -> torch.Tensor:
     return t
 
 
+def rows_per_owner(tokens: int, world: int) -> int:
+    """Rows each rank owns in the fused exchange (the last owner may hold fewer)."""
+    return -(-tokens // world)
+
+
+def owner_of_row(row: int, tokens: int, world: int) -> int:
+    return row // rows_per_owner(tokens, world)
+
+
+class PeerExchange:
+    """The symmetric buffers of one tensor-parallel group and their peer addresses.
+
+    ``slots[b]``: ``(world, rows_per_owner, hidden)`` receive regions (two, used in turn);
+    ``out``: the ``(tokens, hidden)`` layer output every owner writes its rows into;
+    ``flags``: eight words per rank for the barrier.  ``slot_ptrs[b][o]`` is the address, in
+    owner ``o``'s memory, of the region reserved for this rank.
+    """
+
+    def __init__(self, tokens: int, hidden: int, group=None, device=None):
+        import torch.distributed._symmetric_memory as symm
+
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("the peer exchange supports at most 8 ranks")
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.rows = rows_per_owner(tokens, self.world)
+        elem = 2
+        self.slots = [symm.empty((self.world, self.rows, hidden), dtype=torch.bfloat16, device=dev)
+                      for _ in range(2)]
+        self.out = symm.empty((tokens, hidden), dtype=torch.bfloat16, device=dev)
+        self.flags = symm.empty((8,), dtype=torch.int32, device=dev)
+        self.flags.zero_()
+        handles = [symm.rendezvous(t, group) for t in (*self.slots, self.out, self.flags)]
+        mine = self.rank * self.rows * hidden * elem
+        self.slot_ptrs = [[int(p) + mine for p in h.buffer_ptrs] for h in handles[:2]]
+        self.out_ptrs = [int(p) for p in handles[2].buffer_ptrs]
+        self.flag_ptrs = [int(p) for p in handles[3].buffer_ptrs]
+        self._handles = handles
+        self.epoch = 0
+        self.turn = 0
+        torch.cuda.synchronize(dev)
+        dist.barrier(group)          # every rank's flags are zero before the first peer barrier
+
+    def barrier(self):
+        from . import ops
+
+        self.epoch += 1
+        ops.peer_barrier(self.flag_ptrs, self.rank, self.epoch)
+
+
 class TensorParallelMlp:
     """``h + all_reduce(down_g(SwiGLU(gate_up_g(norm(h)))))`` with ``h = x + delta``.
 
@@ -56,7 +116,8 @@ class TensorParallelMlp:
     """
 
     def __init__(self, tokens: int, norm_weight, gate_up_shard, down_shard, eps: float = 1e-6,
-                 group=None, make_layer=None, add=None, slabs: int = 1, reserve_groups: int = 8):
+                 group=None, make_layer=None, add=None, slabs: int = 1, reserve_groups: int = 8,
+                 fused: bool = False):
         if make_layer is None:
             from .layer import Rank7MlpLayer as make_layer
         self.group = group
@@ -66,12 +127,25 @@ class TensorParallelMlp:
         self.out = None
         self.slabs = max(1, int(slabs))
         self.reserve_groups = reserve_groups
+        self.exchange = None
+        if fused:
+            if not (dist.is_available() and dist.is_initialized()):
+                raise RuntimeError("fused tensor parallelism needs an initialised process group")
+            down = self.layer.down_plan
+            m, _, n = down.shape
+            if n % 8 or not down.c.is_contiguous():
+                raise ValueError("the fused exchange needs a hidden size that is a multiple of 8")
+            self.exchange = PeerExchange(m, n, group)
+            gate = self.layer.gate_plan
+            gate.preclear = gate.c                   # nothing to clear: the push GEMM initialises its output
 
     def forward(self, x: torch.Tensor, delta: torch.Tensor | None = None) -> torch.Tensor:
         if delta is None:
             if self._zero is None or self._zero.shape != x.shape:
                 self._zero = torch.zeros_like(x)
             delta = self._zero
+        if self.exchange is not None:
+            return self._forward_fused(x, delta)
         if self.slabs > 1 and hasattr(self.layer, "down_plan") and self.layer.down_plan.c.is_contiguous():
             return self._forward_pipelined(x, delta)
         partial, h = self.layer.chain(delta, x)
@@ -86,6 +160,23 @@ class TensorParallelMlp:
             if self.out is None or self.out.shape != h.shape:
                 self.out = torch.empty_like(h)
             ops.add(h, partial, out=self.out)
+        return self.out
+
+    def _forward_fused(self, x, delta):
+        from . import ops
+
+        lay, ex = self.layer, self.exchange
+        gate, down = lay.gate_plan, lay.down_plan
+        gate(x, delta, lay.norm_weight, lay.eps, prepared_w=lay.gate_bw)
+        m, k, n = down.shape
+        b = ex.turn
+        ex.turn ^= 1
+        ops.gemm_r7_push(down.scheme, down.a_planes(), lay.down_bw, m, n, k, down.c, ex.slot_ptrs[b],
+                         ex.rank, ex.rows, cta_group=down.cta_group)
+        ex.barrier()                 # every rank's pushes have landed
+        ops.reduce_gather(ex.slots[b], gate.residual_out, ex.out_ptrs, ex.rows, ex.rank)
+        ex.barrier()                 # every owner's rows have landed here
+        self.out = ex.out
         return self.out
 
     def _forward_pipelined(self, x, delta):
