@@ -1,6 +1,7 @@
-"""Tensor-parallel layer over NCCL on two GPUs (skipped on a single-GPU box): each rank runs
-the rank-7 chain on its shard, one all-reduce combines the partials, and the result must match
-the unsharded layer and the functional reference."""
+"""Tensor-parallel layer on two GPUs (skipped on a single-GPU box): each rank runs the rank-7
+chain on its shard; the partials are combined by one NCCL all-reduce, by the slab-pipelined
+all-reduce, and by this package's own exchange over peer memory (push from the GEMM kernel,
+barrier, reduce + gather); all must match the unsharded layer and the functional reference."""
 import os
 import socket
 
@@ -43,12 +44,18 @@ def _worker(rank, world, port, ret):
         piped = tp.TensorParallelMlp(m, nw, gu_shard, d_shard, 1e-6, slabs=2)
         out3 = piped(x).clone()                       # down in two slabs, all-reduce overlapped
         out3 = piped(x).clone()
+        fused = tp.TensorParallelMlp(m, nw, gu_shard, d_shard, 1e-6, fused=True)
+        out4 = fused(x).clone()                       # exchange in this package's own kernels
+        out4 = fused(x).clone()
+        out5 = fused(out4.clone(), x).clone()         # a second layer call on the other slot set
+        ref5 = layer(out4.clone(), x).clone()
         full = Rank7MlpLayer(m, nw, wgu, wd, 1e-6)(x)
         dense = DenseMlpLayer(m, nw, wgu, wd, 1e-6, gemm="cublas")(x)
         ops.check_status()
         rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
         branch = lambda y: y.float() - x.float()
-        ret[rank] = (rel(out, full), rel(branch(out), branch(dense)), rel(out2, out), rel(out3, out))
+        ret[rank] = (rel(out, full), rel(branch(out), branch(dense)), rel(out2, out), rel(out3, out),
+                     rel(out4, out), rel(out5, ref5))
     finally:
         dist.destroy_process_group()
 
@@ -62,8 +69,10 @@ def test_two_gpu_tensor_parallel_layer():
         mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
         assert len(ret) == 2
         for rank in range(2):
-            vs_full, branch_vs_dense, repeat, piped = ret[rank]
+            vs_full, branch_vs_dense, repeat, piped, fused, fused_next = ret[rank]
             assert piped < 4e-3, (rank, piped)
+            assert fused < 4e-3, (rank, fused)                   # fp32 sum of the partials vs bf16
+            assert fused_next < 4e-3, (rank, fused_next)
             assert vs_full < 4e-3, (rank, vs_full)               # residual-dominated output
             assert branch_vs_dense < 5e-2, (rank, branch_vs_dense)
             assert repeat < 4e-3, (rank, repeat)

@@ -74,6 +74,10 @@ class PeerExchange:
     """
 
     def __init__(self, tokens: int, hidden: int, group=None, device=None):
+        import os
+
+        # Only plain peer loads and stores are used here: no multicast object is needed.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
 
         group = group if group is not None else dist.group.WORLD
