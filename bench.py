@@ -374,7 +374,8 @@ def run_ours(args, rank, world, device):
     il = cfg["inter"] // world
     x, nw, wgu, wd = make_layer_tensors(cfg["tokens"], cfg["hidden"], cfg["inter"], device,
                                         inter_local=il, rank=rank)
-    layer = TensorParallelMlp(cfg["tokens"], nw, wgu, wd, EPS, slabs=args.slabs)
+    layer = TensorParallelMlp(cfg["tokens"], nw, wgu, wd, EPS, slabs=args.slabs,
+                              fused=args.exchange == "peer")
     launches0 = ops.launch_count()
     with ClockWatch(torch.cuda.current_device()) as cw:
         times = timed_steps(lambda: layer(x), args.steps, args.warmup, flush, sync_all,
@@ -405,7 +406,7 @@ def run_ours(args, rank, world, device):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": _workload_name(world), **cfg, "parallelism": f"tp{world}",
-                       "down_slabs": args.slabs,
+                       "down_slabs": args.slabs, "exchange": args.exchange,
                        "all_reduce_bytes": cfg["tokens"] * cfg["hidden"] * 2,
                        "l2": "flushed between steps (256 MiB memset)"},
             "clocks": cw.summary(),
@@ -588,6 +589,10 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--exchange", choices=("peer", "nccl"), default="nccl",
+                    help="N > 1: how the ranks' partial outputs are combined: 'peer' = pushed from inside "
+                         "the down GEMM over NVLink, then reduce + gather in this package's kernels; "
+                         "'nccl' = one library all-reduce")
     ap.add_argument("--slabs", type=int, default=1,
                     help="N > 1: slabs of the down GEMM pipelined with the all-reduce (1 = no overlap)")
     args = ap.parse_args()
