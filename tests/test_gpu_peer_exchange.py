@@ -62,14 +62,6 @@ def test_push_and_reduce_gather_emulated_ranks(lc, dims):
         assert torch.equal(t, want)
 
 
-def test_owner_arithmetic():
-    from lcgemm import tp
-
-    assert tp.rows_per_owner(8192, 8) == 1024 and tp.rows_per_owner(1030, 8) == 129
-    assert tp.owner_of_row(0, 1030, 8) == 0 and tp.owner_of_row(1029, 1030, 8) == 7
-    assert tp.owner_of_row(128, 1030, 8) == 0 and tp.owner_of_row(129, 1030, 8) == 1
-
-
 def test_push_rejects_bad_arguments(lc):
     sch = lc.load(DOWN)
     a, w = seeded((256, 128), 1), seeded((264, 128), 2)

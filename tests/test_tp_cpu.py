@@ -93,3 +93,15 @@ def test_shard_errors():
     # without a process group the reduction is the identity
     t = torch.ones(3)
     assert tp.all_reduce_sum(t) is t
+
+
+def test_owner_arithmetic_of_the_peer_exchange():
+    from lcgemm import tp
+
+    assert tp.rows_per_owner(8192, 8) == 1024 and tp.rows_per_owner(1030, 8) == 129
+    assert tp.owner_of_row(0, 1030, 8) == 0 and tp.owner_of_row(1029, 1030, 8) == 7
+    assert tp.owner_of_row(128, 1030, 8) == 0 and tp.owner_of_row(129, 1030, 8) == 1
+    # every row has exactly one owner and owners hold contiguous ranges
+    for tokens, world in ((4096, 3), (4096, 4), (1030, 8), (7, 8)):
+        owners = [tp.owner_of_row(r, tokens, world) for r in range(tokens)]
+        assert owners == sorted(owners) and 0 <= owners[0] and owners[-1] < world
