@@ -452,7 +452,7 @@ def run_ours(args, rank, world, device):
                            "them) and its rows of the result back, copies overlapped with compute",
                     "serial_ms_per_step": e2e_serial_ms},
             "gpu_launches": launches * world,
-            "roofline": {"bound": "tensor", "kernel": "whole step (per-rank rank-7 chain + all-reduce)",
+            "roofline": {"bound": "tensor", "kernel": "whole step (per-rank rank-7 chain + exchange)",
                          "achieved": 0.875 * flops / (ms * 1e-3) / 1e12 / world, "peak": peak_burst,
                          "unit": "TFLOP/s per GPU", "frac": 0.875 * flops / (ms * 1e-3) / 1e12 / world / peak_burst,
                          "peak_kind": f"{peak_kind} cuBLAS bf16 burst", "flops_per_launch": per_rank_gate,
@@ -627,7 +627,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    ap.add_argument("--exchange", choices=("peer", "nccl"), default="nccl",
+    ap.add_argument("--exchange", choices=("peer", "nccl"), default="peer",
                     help="N > 1: how the ranks' partial outputs are combined: 'peer' = pushed from inside "
                          "the down GEMM over NVLink, then reduce + gather in this package's kernels; "
                          "'nccl' = one library all-reduce")
