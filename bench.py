@@ -50,7 +50,7 @@ CPU_SAMPLE_TOKENS = 256
 FLUSH_BYTES = 256 << 20
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate_up launch at the headline shape,
 # from the ncu capture summarised in profiles/k_gemm_gate_up_chain.md (4096 tokens).
-GATE_UP_DRAM_TRAFFIC_BYTES = 2_321_533_184   # 1 659 791 360 read + 661 741 824 written
+GATE_UP_DRAM_TRAFFIC_BYTES = 2_218_558_208   # 1 579 047 424 read + 639 510 784 written
 
 
 def layer_flops(tokens, hidden, inter):
@@ -366,7 +366,7 @@ def run_ours(args, rank, world, device):
         gate_ms = head["gate_up_ms"]
         executed = 0.875 * gate_flops / (gate_ms * 1e-3) / 1e12
         roofline = {
-            "bound": "tensor", "kernel": "k_gemm<2,true> (chained rank-7 gate_up, 4096x5120x34816)",
+            "bound": "tensor", "kernel": "k_gemm<2, planes> (chained rank-7 gate_up, 4096x5120x34816)",
             "achieved": executed, "peak": peak_burst, "unit": "TFLOP/s", "frac": executed / peak_burst,
             "peak_kind": f"{peak_kind} cuBLAS bf16 burst; sustained {peak_sustained}",
             "flops_per_launch": 0.875 * gate_flops, "effective_tflops": gate_flops / (gate_ms * 1e-3) / 1e12,
