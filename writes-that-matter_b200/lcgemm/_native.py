@@ -15,7 +15,8 @@ _PKG = Path(__file__).resolve().parent
 CSRC = _PKG.parent / "csrc"
 INCLUDE = _PKG.parent.parent / "include"
 LIB_DIR = _PKG / "_lib"
-LIB_PATH = LIB_DIR / "liblcgemm_b200.so"
+# LCGEMM_B200_LIB points the loader at another build of the same sources (an A/B comparison).
+LIB_PATH = Path(os.environ.get("LCGEMM_B200_LIB") or LIB_DIR / "liblcgemm_b200.so")
 SOURCES = ("lcg_scheme.cu", "lcg_simt.cu", "lcg_gemm.cu", "lcg_static.cu", "lcg_peer.cu")
 
 OK = 0
