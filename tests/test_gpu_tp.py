@@ -49,13 +49,25 @@ def _worker(rank, world, port, ret):
         out4 = fused(x).clone()
         out5 = fused(out4.clone(), x).clone()         # a second layer call on the other slot set
         ref5 = layer(out4.clone(), x).clone()
+        rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+        # host-to-host streaming: every rank feeds its rows of the batch and gets its rows back
+        from lcgemm.streaming import HostStreamedLayer
+        rows = m // world
+        st = HostStreamedLayer(fused, m, h, group=dist.group.WORLD)
+        xs = x[rank * rows:(rank + 1) * rows].cpu().pin_memory()
+        got = [torch.zeros_like(xs).pin_memory() for _ in range(3)]
+        st.begin()
+        for o in got:
+            st.submit(xs, o)
+        st.end()
+        st.drain()
+        streamed = max(rel(o.to(dev), out4[rank * rows:(rank + 1) * rows]) for o in got)
         full = Rank7MlpLayer(m, nw, wgu, wd, 1e-6)(x)
         dense = DenseMlpLayer(m, nw, wgu, wd, 1e-6, gemm="cublas")(x)
         ops.check_status()
-        rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
         branch = lambda y: y.float() - x.float()
         ret[rank] = (rel(out, full), rel(branch(out), branch(dense)), rel(out2, out), rel(out3, out),
-                     rel(out4, out), rel(out5, ref5))
+                     rel(out4, out), rel(out5, ref5), streamed)
     finally:
         dist.destroy_process_group()
 
@@ -69,7 +81,8 @@ def test_two_gpu_tensor_parallel_layer():
         mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
         assert len(ret) == 2
         for rank in range(2):
-            vs_full, branch_vs_dense, repeat, piped, fused, fused_next = ret[rank]
+            vs_full, branch_vs_dense, repeat, piped, fused, fused_next, streamed = ret[rank]
+            assert streamed < 4e-3, (rank, streamed)
             assert piped < 4e-3, (rank, piped)
             assert fused < 4e-3, (rank, fused)                   # fp32 sum of the partials vs bf16
             assert fused_next < 4e-3, (rank, fused_next)
