@@ -77,6 +77,59 @@ __device__ __forceinline__ void signed_sum(const TermTable& tt, int r, const flo
   }
 }
 
+// A coefficient table whose entries are all -1, 0 or +1, packed two bits per entry (entry
+// r * 4 + x at bit 2 * (r * 4 + x): 0 = zero, 1 = +1, 3 = -1).  Kernels templated on the packed
+// code see the table at compile time: the signed sums become straight adds and subtracts with
+// no table loads, compares or branches (these kernels are bound by instruction issue).
+__host__ __device__ constexpr int code_coef(unsigned long long code, int r, int x) {
+  return static_cast<int>((code >> (2 * (r * 4 + x))) & 3ull);
+}
+constexpr unsigned long long pack_code(const int (&t)[kMaxRank][4]) {
+  unsigned long long code = 0;
+  for (int r = 0; r < kMaxRank; ++r)
+    for (int x = 0; x < 4; ++x)
+      code |= static_cast<unsigned long long>(t[r][x] == 0 ? 0 : (t[r][x] > 0 ? 1 : 3)) << (2 * (r * 4 + x));
+  return code;
+}
+// The A-side tables of the two schemes this package ships (lcgemm/schemes/*.json).
+constexpr int kTablePostsumA[kMaxRank][4] = {{0, 1, 0, 0},  {1, 0, 0, 0}, {0, 1, 1, -1}, {0, 1, 0, -1},
+                                             {0, 0, 1, -1}, {0, 0, 1, 0}, {1, -1, -1, 1}};
+constexpr int kTableLocalityA[kMaxRank][4] = {{-1, 0, 1, 0}, {0, 0, 1, 1}, {0, 0, 0, 1}, {1, 0, 0, 1},
+                                              {1, 0, 0, 0},  {1, 1, 0, 0}, {0, 1, 0, -1}};
+constexpr unsigned long long kCodePostsumA = pack_code(kTablePostsumA);
+constexpr unsigned long long kCodeLocalityA = pack_code(kTableLocalityA);
+
+// Same result as signed_sum (starts from +0, block order), table known at compile time.
+template <unsigned long long kCode>
+__device__ __forceinline__ void signed_sum_fixed(int r, const float (&blk)[4][8], float (&out)[8]) {
+#pragma unroll
+  for (int t = 0; t < 8; ++t) out[t] = 0.f;
+#pragma unroll
+  for (int x = 0; x < 4; ++x) {
+    const int c = code_coef(kCode, r, x);      // a constant once the caller's loop over r is unrolled
+    if (c == 1) {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) out[t] = out[t] + blk[x][t];
+    } else if (c == 3) {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) out[t] = out[t] - blk[x][t];
+    }
+  }
+}
+
+// 0 when the table is not one of the compiled ones (or has an entry outside {-1, 0, 1}).
+unsigned long long table_code(const TermTable& t, int rank) {
+  if (rank != kMaxRank) return 0;
+  unsigned long long code = 0;
+  for (int r = 0; r < kMaxRank; ++r)
+    for (int x = 0; x < 4; ++x) {
+      const float v = t.coef[r][x];
+      if (v != 0.f && v != 1.f && v != -1.f) return 0;
+      code |= static_cast<unsigned long long>(v == 0.f ? 0 : (v > 0.f ? 1 : 3)) << (2 * (r * 4 + x));
+    }
+  return code;
+}
+
 // ------------------------------------------------------------------ planes
 // One thread per (block row, 8-column vector).  `transposed_blocks` selects the
 // block indexing: A planes combine src[i*R2 + row, k*K2 + col] with table index
@@ -208,7 +261,8 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src)
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
 }
 
-__global__ void __launch_bounds__(512)
+template <unsigned long long kCode>      // 0: the table comes at run time in `tt`
+__global__ void __launch_bounds__(512, 2)  // 64 registers: three 320-thread CTAs fit an SM
 k_norm_planes_staged(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __restrict__ residual,
                      const __nv_bfloat16* __restrict__ norm_w, int m2, int k, float eps, int rank,
                      TermTable tt, __nv_bfloat16* residual_out, __nv_bfloat16* __restrict__ out,
@@ -284,10 +338,21 @@ k_norm_planes_staged(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat1
         for (int e = 0; e < 8; ++e) y[i * 2 + kb][e] = hf[e] * rstd[i] * (w[e] + 1.0f);
       }
     }
-    for (int r = 0; r < rank; ++r) {
-      float o[8];
-      signed_sum(tt, r, y, o);
-      *reinterpret_cast<Vec8*>(out + (static_cast<size_t>(r) * m2 + rho) * ld_out + v * 8) = pack8(o);
+    if constexpr (kCode != 0) {
+      __nv_bfloat16* dst = out + static_cast<size_t>(rho) * ld_out + v * 8;
+      const size_t plane_stride = static_cast<size_t>(m2) * ld_out;
+#pragma unroll
+      for (int r = 0; r < kMaxRank; ++r) {
+        float o[8];
+        signed_sum_fixed<kCode>(r, y, o);
+        *reinterpret_cast<Vec8*>(dst + r * plane_stride) = pack8(o);
+      }
+    } else {
+      for (int r = 0; r < rank; ++r) {
+        float o[8];
+        signed_sum(tt, r, y, o);
+        *reinterpret_cast<Vec8*>(out + (static_cast<size_t>(r) * m2 + rho) * ld_out + v * 8) = pack8(o);
+      }
     }
   }
 }
@@ -478,15 +543,24 @@ extern "C" int lcg_norm_planes(const lcg_scheme_t* scheme, const void* delta, co
     static bool configured[64] = {};
     int dev = 0;
     LCG_CUDA_OK(cudaGetDevice(&dev));
+    const TermTable table = a_table(scheme);
+    const unsigned long long code = table_code(table, scheme->rank);
+    auto kern = code == kCodePostsumA    ? k_norm_planes_staged<kCodePostsumA>
+                : code == kCodeLocalityA ? k_norm_planes_staged<kCodeLocalityA>
+                                         : k_norm_planes_staged<0>;
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-      LCG_CUDA_OK(cudaFuncSetAttribute(k_norm_planes_staged, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      LCG_CUDA_OK(cudaFuncSetAttribute(k_norm_planes_staged<kCodePostsumA>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
+      LCG_CUDA_OK(cudaFuncSetAttribute(k_norm_planes_staged<kCodeLocalityA>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
+      LCG_CUDA_OK(cudaFuncSetAttribute(k_norm_planes_staged<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        72 * 1024));
       if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    k_norm_planes_staged<<<static_cast<unsigned>(M / 2), threads, smem, static_cast<cudaStream_t>(stream)>>>(
+    kern<<<static_cast<unsigned>(M / 2), threads, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(residual),
         static_cast<const __nv_bfloat16*>(norm_weight), static_cast<int>(M / 2), static_cast<int>(K), eps,
-        scheme->rank, a_table(scheme), static_cast<__nv_bfloat16*>(residual_out),
+        scheme->rank, table, static_cast<__nv_bfloat16*>(residual_out),
         static_cast<__nv_bfloat16*>(out), static_cast<int>(ld_out));
     LCG_CUDA_OK(cudaGetLastError());
     count_launch();
