@@ -50,6 +50,41 @@ struct TermTable {
   float coef[kMaxRank][4];
 };
 
+// A coefficient table whose entries are all -1, 0 or +1, packed two bits per entry (entry
+// r * 4 + x at bit 2 * (r * 4 + x): 0 = zero, 1 = +1, 3 = -1).  Kernels templated on the packed
+// code see the table at compile time: the signed sums become straight adds and subtracts with
+// no table loads, compares or branches (these kernels are bound by instruction issue).
+__host__ __device__ constexpr int code_coef(unsigned long long code, int r, int x) {
+  return static_cast<int>((code >> (2 * (r * 4 + x))) & 3ull);
+}
+constexpr unsigned long long pack_code(const int (&t)[kMaxRank][4]) {
+  unsigned long long code = 0;
+  for (int r = 0; r < kMaxRank; ++r)
+    for (int x = 0; x < 4; ++x)
+      code |= static_cast<unsigned long long>(t[r][x] == 0 ? 0 : (t[r][x] > 0 ? 1 : 3)) << (2 * (r * 4 + x));
+  return code;
+}
+// The A-side tables of the two schemes this package ships (lcgemm/schemes/*.json).
+constexpr int kTablePostsumA[kMaxRank][4] = {{0, 1, 0, 0},  {1, 0, 0, 0}, {0, 1, 1, -1}, {0, 1, 0, -1},
+                                             {0, 0, 1, -1}, {0, 0, 1, 0}, {1, -1, -1, 1}};
+constexpr int kTableLocalityA[kMaxRank][4] = {{-1, 0, 1, 0}, {0, 0, 1, 1}, {0, 0, 0, 1}, {1, 0, 0, 1},
+                                              {1, 0, 0, 0},  {1, 1, 0, 0}, {0, 1, 0, -1}};
+constexpr unsigned long long kCodePostsumA = pack_code(kTablePostsumA);
+constexpr unsigned long long kCodeLocalityA = pack_code(kTableLocalityA);
+
+// 0 when the table is not all -1 / 0 / +1 or not of full rank; else its packed code.
+inline unsigned long long table_code(const TermTable& t, int rank) {
+  if (rank != kMaxRank) return 0;
+  unsigned long long code = 0;
+  for (int r = 0; r < kMaxRank; ++r)
+    for (int x = 0; x < 4; ++x) {
+      const float v = t.coef[r][x];
+      if (v != 0.f && v != 1.f && v != -1.f) return 0;
+      code |= static_cast<unsigned long long>(v == 0.f ? 0 : (v > 0.f ? 1 : 3)) << (2 * (r * 4 + x));
+    }
+  return code;
+}
+
 }  // namespace lcg
 
 // The opaque handle of the C ABI.

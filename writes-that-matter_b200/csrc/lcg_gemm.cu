@@ -226,6 +226,7 @@ __device__ __forceinline__ float silu_dev(float g) { return __fdividef(g, 1.0f +
 // each block row of Z, S columns [tn * 256, tn * 256 + 256) of the gate and the up block, read
 // L2-hot; plane columns [tn * 128, +128).  256 threads: 16 slots across (chunk pair, 8-column
 // vector), 16 rows per pass, two passes (16 x 16-byte loads per thread) in flight at a time.
+template <unsigned long long kCode>   // packed coefficient table known at compile time, or 0
 __device__ __forceinline__ void plane_rows32(const ChainParams& ch, int tn, int row0, int ptid) {
   const int slot = ptid & 15;
   const int pair = slot >> 3;
@@ -263,19 +264,9 @@ __device__ __forceinline__ void plane_rows32(const ChainParams& ch, int tn, int 
         unpack_bf16x8(q[t][i][0][hh], g);
         unpack_bf16x8(q[t][i][1][hh], uu);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) sv[i * 2 + hh][e] = silu_dev(g[e]) * uu[e];
+        for (int e = 0; e < 8; ++e) sv[i * 2 + hh][e] = __fmul_rn(silu_dev(g[e]), uu[e]);   // never fused into the sums
       }
-    for (int r = 0; r < ch.plane_rank; ++r) {
-      float o[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) o[e] = 0.f;
-#pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const float w = ch.plane_terms.coef[r][x];
-        if (w == 0.f) continue;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = fmaf(w, sv[x][e], o[e]);
-      }
+    auto store_plane = [&](int r, const float (&o)[8]) {
       uint4 outv;
       outv.x = pack_bf16x2(o[0], o[1]);
       outv.y = pack_bf16x2(o[2], o[3]);
@@ -283,6 +274,41 @@ __device__ __forceinline__ void plane_rows32(const ChainParams& ch, int tn, int 
       outv.w = pack_bf16x2(o[6], o[7]);
       *reinterpret_cast<uint4*>(ch.planes + (static_cast<int64_t>(r) * ch.m2 + rho[t]) * ch.ld_planes +
                                 pcol) = outv;
+    };
+    if constexpr (kCode != 0) {
+      // Straight adds and subtracts: same sums as below (start from +0, block order).
+#pragma unroll
+      for (int r = 0; r < kMaxRank; ++r) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = 0.f;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const int c = code_coef(kCode, r, x);
+          if (c == 1) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = __fadd_rn(o[e], sv[x][e]);
+          } else if (c == 3) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = __fsub_rn(o[e], sv[x][e]);
+          }
+        }
+        store_plane(r, o);
+      }
+    } else {
+      for (int r = 0; r < ch.plane_rank; ++r) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = 0.f;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const float w = ch.plane_terms.coef[r][x];
+          if (w == 0.f) continue;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = fmaf(w, sv[x][e], o[e]);
+        }
+        store_plane(r, o);
+      }
     }
   }
 }
@@ -326,7 +352,7 @@ __device__ __forceinline__ void push_rows32(const PushParams& pp, int tn, int ro
 // kMode: 0 plain GEMM; 1 chained (plane warps form SwiGLU + the consumer's planes behind each
 // tile); 2 push (the same warps copy each finished tile to the rank that owns its rows).
 constexpr int kModePlain = 0, kModePlanes = 1, kModePush = 2;
-template <int kCtaGroup, int kMode>
+template <int kCtaGroup, int kMode, unsigned long long kPlaneCode = 0>
 __global__ void __launch_bounds__(kMode != kModePlain ? kThreadsChain : kThreadsPlain, 1)
 k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
        const __grid_constant__ CMaps tma_c, const __grid_constant__ GemmParams p) {
@@ -606,7 +632,8 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
           for (int step = 0; step < kBM / 32; ++step) push_rows32(p.push, tn, row_base + step * 32, ptid);
         } else {
 #pragma unroll 1
-          for (int step = 0; step < kBM / 32; ++step) plane_rows32(ch, tn, row_base + step * 32, ptid);
+          for (int step = 0; step < kBM / 32; ++step)
+            plane_rows32<kPlaneCode>(ch, tn, row_base + step * 32, ptid);
         }
       }
       // every plane thread has read its ring entry: the epilogue may reuse it
@@ -669,6 +696,7 @@ k_zero_tail_tiles(const __grid_constant__ GemmParams p, const ZeroArgs z) {
 // launch, behind the GEMM kernel (their C blocks are sums over several CTAs and final only when
 // it ends).  One CTA per 32 rows
 // of a tile: grid = tail tiles * tile_m / 32, 256 threads.
+template <unsigned long long kPlaneCode>
 __global__ void __launch_bounds__(kPlaneThreads)
 k_tail_planes(const __grid_constant__ GemmParams p, const int tile_m) {
   const int chunks = tile_m / 32;
@@ -679,7 +707,7 @@ k_tail_planes(const __grid_constant__ GemmParams p, const int tile_m) {
   if (p.push.world > 0)
     push_rows32(p.push, tn, tm * tile_m + c * 32, static_cast<int>(threadIdx.x));
   else
-    plane_rows32(p.chain, tn, tm * tile_m + c * 32, static_cast<int>(threadIdx.x));
+    plane_rows32<kPlaneCode>(p.chain, tn, tm * tile_m + c * 32, static_cast<int>(threadIdx.x));
 }
 
 // ============================================================== host side
@@ -754,12 +782,12 @@ int pick_group_m(int tiles_m, int groups) {
   return best;
 }
 
-template <int kCtaGroup, int kMode>
+template <int kCtaGroup, int kMode, unsigned long long kPlaneCode = 0>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CMaps& mc, GemmParams& p,
            cudaStream_t stream) {
   using T = Tile<kCtaGroup>;
   constexpr bool kChain = kMode != kModePlain;
-  auto kern = k_gemm<kCtaGroup, kMode>;
+  auto kern = k_gemm<kCtaGroup, kMode, kPlaneCode>;
   static bool configured[64] = {};   // per device: the attribute belongs to the device's context
   int dev = 0;
   LCG_CUDA_OK(cudaGetDevice(&dev));
@@ -1062,11 +1090,22 @@ extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t*
   ch.preclear_vecs = preclear_bytes / 16;
   auto st_ = static_cast<cudaStream_t>(stream);
   if (int e = zero_tail_tiles(p, z, ldz, M, N, g, cta_group, st_)) return e;
-  if (int e = cta_group == 1 ? launch<1, kModePlanes>(ma, mb, mc, p, st_) : launch<2, kModePlanes>(ma, mb, mc, p, st_))
-    return e;
+  // The plane phase is compiled for the shipped `down` scheme's A table; any other table runs
+  // the same kernel with the table read at run time.
+  const bool fixed = table_code(ch.plane_terms, plane_scheme->rank) == kCodeLocalityA;
+  int e = LCG_OK;
+  if (cta_group == 1)
+    e = fixed ? launch<1, kModePlanes, kCodeLocalityA>(ma, mb, mc, p, st_) : launch<1, kModePlanes>(ma, mb, mc, p, st_);
+  else
+    e = fixed ? launch<2, kModePlanes, kCodeLocalityA>(ma, mb, mc, p, st_) : launch<2, kModePlanes>(ma, mb, mc, p, st_);
+  if (e) return e;
   if (p.tail_tiles > 0) {
     const int tile_m = kBM * cta_group;
-    k_tail_planes<<<p.tail_tiles * (tile_m / 32), kPlaneThreads, 0, st_>>>(p, tile_m);
+    const unsigned tail_grid = static_cast<unsigned>(p.tail_tiles * (tile_m / 32));
+    if (fixed)
+      k_tail_planes<kCodeLocalityA><<<tail_grid, kPlaneThreads, 0, st_>>>(p, tile_m);
+    else
+      k_tail_planes<0><<<tail_grid, kPlaneThreads, 0, st_>>>(p, tile_m);
     LCG_CUDA_OK(cudaGetLastError());
     count_launch();
   }
@@ -1120,7 +1159,7 @@ extern "C" int lcg_gemm_r7_push(const lcg_scheme_t* scheme, const void* a_planes
     return e;
   if (p.tail_tiles > 0) {
     const int tile_m = kBM * cta_group;
-    k_tail_planes<<<p.tail_tiles * (tile_m / 32), kPlaneThreads, 0, st_>>>(p, tile_m);
+    k_tail_planes<0><<<p.tail_tiles * (tile_m / 32), kPlaneThreads, 0, st_>>>(p, tile_m);
     LCG_CUDA_OK(cudaGetLastError());
     count_launch();
   }

@@ -77,28 +77,6 @@ __device__ __forceinline__ void signed_sum(const TermTable& tt, int r, const flo
   }
 }
 
-// A coefficient table whose entries are all -1, 0 or +1, packed two bits per entry (entry
-// r * 4 + x at bit 2 * (r * 4 + x): 0 = zero, 1 = +1, 3 = -1).  Kernels templated on the packed
-// code see the table at compile time: the signed sums become straight adds and subtracts with
-// no table loads, compares or branches (these kernels are bound by instruction issue).
-__host__ __device__ constexpr int code_coef(unsigned long long code, int r, int x) {
-  return static_cast<int>((code >> (2 * (r * 4 + x))) & 3ull);
-}
-constexpr unsigned long long pack_code(const int (&t)[kMaxRank][4]) {
-  unsigned long long code = 0;
-  for (int r = 0; r < kMaxRank; ++r)
-    for (int x = 0; x < 4; ++x)
-      code |= static_cast<unsigned long long>(t[r][x] == 0 ? 0 : (t[r][x] > 0 ? 1 : 3)) << (2 * (r * 4 + x));
-  return code;
-}
-// The A-side tables of the two schemes this package ships (lcgemm/schemes/*.json).
-constexpr int kTablePostsumA[kMaxRank][4] = {{0, 1, 0, 0},  {1, 0, 0, 0}, {0, 1, 1, -1}, {0, 1, 0, -1},
-                                             {0, 0, 1, -1}, {0, 0, 1, 0}, {1, -1, -1, 1}};
-constexpr int kTableLocalityA[kMaxRank][4] = {{-1, 0, 1, 0}, {0, 0, 1, 1}, {0, 0, 0, 1}, {1, 0, 0, 1},
-                                              {1, 0, 0, 0},  {1, 1, 0, 0}, {0, 1, 0, -1}};
-constexpr unsigned long long kCodePostsumA = pack_code(kTablePostsumA);
-constexpr unsigned long long kCodeLocalityA = pack_code(kTableLocalityA);
-
 // Same result as signed_sum (starts from +0, block order), table known at compile time.
 template <unsigned long long kCode>
 __device__ __forceinline__ void signed_sum_fixed(int r, const float (&blk)[4][8], float (&out)[8]) {
@@ -109,31 +87,19 @@ __device__ __forceinline__ void signed_sum_fixed(int r, const float (&blk)[4][8]
     const int c = code_coef(kCode, r, x);      // a constant once the caller's loop over r is unrolled
     if (c == 1) {
 #pragma unroll
-      for (int t = 0; t < 8; ++t) out[t] = out[t] + blk[x][t];
+      for (int t = 0; t < 8; ++t) out[t] = __fadd_rn(out[t], blk[x][t]);   // never contracted
     } else if (c == 3) {
 #pragma unroll
-      for (int t = 0; t < 8; ++t) out[t] = out[t] - blk[x][t];
+      for (int t = 0; t < 8; ++t) out[t] = __fsub_rn(out[t], blk[x][t]);
     }
   }
-}
-
-// 0 when the table is not one of the compiled ones (or has an entry outside {-1, 0, 1}).
-unsigned long long table_code(const TermTable& t, int rank) {
-  if (rank != kMaxRank) return 0;
-  unsigned long long code = 0;
-  for (int r = 0; r < kMaxRank; ++r)
-    for (int x = 0; x < 4; ++x) {
-      const float v = t.coef[r][x];
-      if (v != 0.f && v != 1.f && v != -1.f) return 0;
-      code |= static_cast<unsigned long long>(v == 0.f ? 0 : (v > 0.f ? 1 : 3)) << (2 * (r * 4 + x));
-    }
-  return code;
 }
 
 // ------------------------------------------------------------------ planes
 // One thread per (block row, 8-column vector).  `transposed_blocks` selects the
 // block indexing: A planes combine src[i*R2 + row, k*K2 + col] with table index
 // i*2 + k; B planes combine src[j*R2 + row, k*K2 + col] with table index k*2 + j.
+template <unsigned long long kCode>      // 0: the table comes at run time in `tt`
 __global__ void __launch_bounds__(128)
 k_planes(const __nv_bfloat16* __restrict__ src, int64_t rows, int64_t cols, int64_t ld,
          int64_t rows2, int64_t k2, int64_t k2p, int rank, TermTable tt, bool b_side,
@@ -153,10 +119,19 @@ k_planes(const __nv_bfloat16* __restrict__ src, int64_t rows, int64_t cols, int6
       // a column past this block's K2 is zero even when the matrix continues
       load8_guarded(src, ld, rows, cols, rb * rows2 + row, c0, (col < k2) ? lim : 0, vec_ok, blk[x]);
     }
-  for (int r = 0; r < rank; ++r) {
-    float o[8];
-    signed_sum(tt, r, blk, o);
-    *reinterpret_cast<Vec8*>(out + (r * rows2 + row) * ld_out + col) = pack8(o);
+  if constexpr (kCode != 0) {
+#pragma unroll
+    for (int r = 0; r < kMaxRank; ++r) {
+      float o[8];
+      signed_sum_fixed<kCode>(r, blk, o);
+      *reinterpret_cast<Vec8*>(out + (r * rows2 + row) * ld_out + col) = pack8(o);
+    }
+  } else {
+    for (int r = 0; r < rank; ++r) {
+      float o[8];
+      signed_sum(tt, r, blk, o);
+      *reinterpret_cast<Vec8*>(out + (r * rows2 + row) * ld_out + col) = pack8(o);
+    }
   }
 }
 
@@ -494,10 +469,15 @@ int launch_planes(const lcg_scheme* scheme, const void* src, int64_t rows, int64
   const bool vec_ok = aligned16(src) && ld % 8 == 0 && k2 % 8 == 0;
   const int64_t nvec = k2p / 8;
   dim3 grid(static_cast<unsigned>(rows2), static_cast<unsigned>((nvec + 127) / 128));
-  k_planes<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(src), rows, cols, ld, rows2, k2, k2p, scheme->rank,
-      b_side ? b_table(scheme) : a_table(scheme), b_side, vec_ok,
-      static_cast<__nv_bfloat16*>(out), ld_out);
+  const TermTable table = b_side ? b_table(scheme) : a_table(scheme);
+  // The A side runs per forward pass of the bare GEMM: compiled for the shipped tables.  (The B
+  // side is the offline weight transform.)
+  const unsigned long long code = b_side ? 0 : table_code(table, scheme->rank);
+  auto kern = code == kCodePostsumA ? k_planes<kCodePostsumA>
+              : code == kCodeLocalityA ? k_planes<kCodeLocalityA> : k_planes<0>;
+  kern<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), rows, cols, ld, rows2, k2, k2p, scheme->rank, table,
+      b_side, vec_ok, static_cast<__nv_bfloat16*>(out), ld_out);
   LCG_CUDA_OK(cudaGetLastError());
   count_launch();
   return LCG_OK;
