@@ -13,13 +13,18 @@ N = 1   one "step" = one fused MLP layer of the single-layer configuration
         interleaved in the same process for the speedup figures, and 2048 / 8192 tokens are
         measured beside the headline 4096.
 N > 1   the tensor-parallel configuration (8192 tokens, hidden 8192, intermediate 28672)
-        split over the intermediate dimension, one NCCL all-reduce per layer; total work is
-        fixed as N grows ("strong" scaling).  One process per GPU under torchrun.
+        split over the intermediate dimension; the ranks' partial outputs are combined by
+        the package's own kernels over NVLink peer memory (--exchange peer: pushed from inside
+        the down GEMM, reduced and gathered after a barrier) or by one NCCL all-reduce per
+        layer (--exchange nccl); total work is fixed as N grows ("strong" scaling).  One
+        process per GPU under torchrun.
 
 Timing: CUDA events on the launching stream around every step, L2 flushed (256 MiB memset)
-between steps outside the timed region, max over ranks.  `e2e` repeats the measurement
-through the public layer call with the step's input in pinned host memory and the result
-read back to the host inside the timed region.
+between steps outside the timed region, max over ranks.  `e2e` measures K steps host to host
+through lcgemm.streaming.HostStreamedLayer: every step's input comes from pinned host memory
+and its result goes back to the host inside the timed region, the copies of neighbouring
+steps overlapping the compute; the figure with copy, compute and copy one after the other
+is reported beside it (`serial_ms_per_step`).
 
 --impl reference times the CPU evaluation of the same scheme (the oracle port of the
 reference's torch functions) on the host cores, on a bounded row sample of the workload.
