@@ -263,7 +263,7 @@ def _workload_name(gpus):
 
 
 # --------------------------------------------------------------------- our arm
-def bench_layer_arms(tokens, hidden, inter, steps, warmup, flush, device, with_parts=False):
+def bench_layer_arms(tokens, hidden, inter, steps, warmup, flush, device, with_parts=False, graphs=True):
     """Rank-7 layer and the two dense arms, interleaved step by step.  Returns a dict of
     median / mean ms per arm, and (optionally) the gate_up GEMM's own duration."""
     from lcgemm import ops
@@ -296,7 +296,26 @@ def bench_layer_arms(tokens, hidden, inter, steps, warmup, flush, device, with_p
         for _ in range(warmup):
             fn()
     torch.cuda.synchronize()
-    collecting[0] = True
+    launches_per_step = 0
+    if graphs:
+        # Every arm as one CUDA graph replay per step (the same kernels, launched once); the
+        # gate_up GEMM's own duration comes from a few eager steps, where events can sit inside.
+        from lcgemm.layer import CapturedLayer
+
+        if with_parts:
+            collecting[0] = True
+            for _ in range(max(3, steps // 2)):
+                flush.zero_()
+                r7_step()
+            collecting[0] = False
+            torch.cuda.synchronize()
+        before = ops.launch_count()
+        r7(x), dn(x)
+        launches_per_step = ops.launch_count() - before
+        arms = {"rank7": CapturedLayer(r7, x), "dense_tcgen05": CapturedLayer(dn, x),
+                "dense_cublas": CapturedLayer(cb, x)}
+    else:
+        collecting[0] = True
     launches0 = ops.launch_count()
     times = {k: [] for k in arms}
     for _ in range(steps):
@@ -311,7 +330,7 @@ def bench_layer_arms(tokens, hidden, inter, steps, warmup, flush, device, with_p
     torch.cuda.synchronize()
     ops.check_status()
     res = {k: {"mean_ms": statistics.mean(v), "median_ms": statistics.median(v)} for k, v in times.items()}
-    res["launches"] = ops.launch_count() - launches0
+    res["launches"] = launches_per_step * steps if graphs else ops.launch_count() - launches0
     if with_parts:
         res["gate_up_ms"] = statistics.mean(e0.elapsed_time(e1) for e0, e1 in part_events)
     res["objects"] = (r7, x)
@@ -335,7 +354,7 @@ def run_ours(args, rank, world, device):
         cfg = SINGLE
         with ClockWatch(torch.cuda.current_device()) as cw:
             head = bench_layer_arms(cfg["tokens"], cfg["hidden"], cfg["inter"], args.steps, args.warmup,
-                                    flush, device, with_parts=True)
+                                    flush, device, with_parts=True, graphs=args.graphs)
         clocks = cw.summary()
         r7, x = head.pop("objects")
         ms = head["rank7"]["mean_ms"]
@@ -360,7 +379,7 @@ def run_ours(args, rank, world, device):
             del r7, x
             torch.cuda.empty_cache()
             sub = bench_layer_arms(tokens, cfg["hidden"], cfg["inter"], max(5, args.steps // 2),
-                                   args.warmup, flush, device)
+                                   args.warmup, flush, device, graphs=args.graphs)
             r7, x = sub.pop("objects")
             by_tokens[str(tokens)] = _arm_summary(sub, layer_flops(tokens, cfg["hidden"], cfg["inter"]))
         by_tokens[str(cfg["tokens"])] = _arm_summary(head, flops)
@@ -382,6 +401,8 @@ def run_ours(args, rank, world, device):
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": _workload_name(1), **cfg, "l2": "flushed between steps (256 MiB memset)",
+                       "launch": ("one CUDA graph replay per step, every arm" if args.graphs
+                                  else "eager kernel launches"),
                        "schemes": {"gate_up": "2x2_postsum_cse", "down": "2x2_locality_ordered"}},
             "clocks": clocks,
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
@@ -632,6 +653,8 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--no-graphs", dest="graphs", action="store_false",
+                    help="N = 1: launch the layer's kernels one by one instead of replaying a CUDA graph")
     ap.add_argument("--exchange", choices=("peer", "nccl"), default="peer",
                     help="N > 1: how the ranks' partial outputs are combined: 'peer' = pushed from inside "
                          "the down GEMM over NVLink, then reduce + gather in this package's kernels; "

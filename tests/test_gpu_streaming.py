@@ -36,3 +36,27 @@ def test_streamed_batches_match_direct_calls():
     st.end()
     st.drain()
     assert rel_fro(outs[0], want[2]) <= 8e-3
+
+
+def test_captured_layer_replays_the_same_kernels():
+    from lcgemm import ops
+    from lcgemm.layer import CapturedLayer, DenseMlpLayer, Rank7MlpLayer
+
+    m, h, i = 512, 256, 1024
+    nw, wgu, wd = seeded((h,), 3, 0.01), seeded((2 * i, h), 4, 0.02), seeded((h, i), 5, 0.02)
+    x = seeded((m, h), 60)
+    for layer in (Rank7MlpLayer(m, nw, wgu, wd), DenseMlpLayer(m, nw, wgu, wd)):
+        want = layer(x).clone()
+        before = ops.launch_count()
+        graph = CapturedLayer(layer, x)
+        recorded = ops.launch_count() - before          # warm-up calls + the recorded one
+        for _ in range(3):
+            got = graph()
+        assert ops.launch_count() - before == recorded  # replays go through no host-side launch
+        assert rel_fro(got, want) <= 8e-3
+        x2 = seeded((m, h), 61)
+        want2 = layer(x2).clone()
+        x.copy_(x2)                                      # the recording reads x's storage
+        assert rel_fro(graph(), want2) <= 8e-3
+        x.copy_(seeded((m, h), 60))
+    ops.check_status()

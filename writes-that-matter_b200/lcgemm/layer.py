@@ -93,3 +93,31 @@ class DenseMlpLayer:
 
     __call__ = forward
     launches_per_forward = 5
+
+
+class CapturedLayer:
+    """One layer call recorded into a CUDA graph and replayed: a single launch per step in place
+    of the layer's five or six, which removes the host's launch latency and most of the gaps
+    between the dependent kernels (about 20 us of a 1.4 ms layer).  The input tensor's storage
+    is part of the recording: the caller refills ``x`` in place between replays.  Every kernel
+    of this package can be captured (tensor maps are kernel parameters, nothing allocates or
+    synchronises); attributes that are set on first use are set by the warm-up calls here.
+    """
+
+    def __init__(self, layer, x: torch.Tensor, delta: torch.Tensor | None = None, warmup: int = 3):
+        self.layer, self.x, self.delta = layer, x, delta
+        call = (lambda: layer(x)) if delta is None else (lambda: layer(x, delta))
+        side = torch.cuda.Stream(x.device)
+        side.wait_stream(torch.cuda.current_stream(x.device))
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                call()
+        torch.cuda.current_stream(x.device).wait_stream(side)
+        torch.cuda.synchronize(x.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out = call()
+
+    def __call__(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.out
