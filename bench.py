@@ -431,10 +431,17 @@ def run_ours(args, rank, world, device):
     layer = TensorParallelMlp(cfg["tokens"], nw, wgu, wd, EPS, slabs=args.slabs,
                               fused=args.exchange == "peer")
     launches0 = ops.launch_count()
+    layer(x)
+    launches = (ops.launch_count() - launches0) * args.steps
+    step = lambda: layer(x)
+    graphed = args.graphs and args.exchange == "peer"
+    if graphed:      # the whole layer, exchange included, as one CUDA graph replay per step
+        from lcgemm.tp import CapturedTensorParallel
+
+        step = CapturedTensorParallel(layer, x)
     with ClockWatch(torch.cuda.current_device()) as cw:
-        times = timed_steps(lambda: layer(x), args.steps, args.warmup, flush, sync_all,
+        times = timed_steps(step, args.steps, args.warmup, flush, sync_all,
                             pre_step=(lambda: dist.barrier()))
-    launches = ops.launch_count() - launches0
     ops.check_status()
     x_host = x.cpu().pin_memory()
     out_host = torch.empty_like(x_host).pin_memory()
@@ -467,6 +474,7 @@ def run_ours(args, rank, world, device):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": _workload_name(world), **cfg, "parallelism": f"tp{world}",
                        "down_slabs": args.slabs, "exchange": args.exchange,
+                       "launch": "one CUDA graph replay per step" if graphed else "eager kernel launches",
                        "all_reduce_bytes": cfg["tokens"] * cfg["hidden"] * 2,
                        "l2": "flushed between steps (256 MiB memset)"},
             "clocks": cw.summary(),
@@ -654,7 +662,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-graphs", dest="graphs", action="store_false",
-                    help="N = 1: launch the layer's kernels one by one instead of replaying a CUDA graph")
+                    help="launch the layer's kernels one by one instead of replaying a CUDA graph")
     ap.add_argument("--exchange", choices=("peer", "nccl"), default="peer",
                     help="N > 1: how the ranks' partial outputs are combined: 'peer' = pushed from inside "
                          "the down GEMM over NVLink, then reduce + gather in this package's kernels; "

@@ -207,9 +207,11 @@ int lcg_gemm_r7_push(const lcg_scheme_t* scheme, const void* a_planes, int64_t l
                      int64_t rows_per_owner, int cta_group, int32_t* status, void* stream);
 
 /* Barrier between the ranks, on the stream: flags is a host array of `world` device pointers,
- * flags[r] = rank r's array of 8 uint32 words (zero before the first barrier), peer-mapped.
+ * flags[r] = rank r's array of 16 uint32 words (zero before the first barrier), peer-mapped.
  * Rank `rank` writes `epoch` into word `rank` of every rank's array and waits until its own
- * array holds `epoch` or more in every word; epochs must grow from call to call.  The wait
+ * array holds `epoch` or more in every word; epochs must grow from call to call.  With
+ * epoch = 0 the kernel counts the calls itself (in word 8 of the rank's own array; every rank
+ * must then use 0 for every barrier), which lets a CUDA graph replay the launch.  The wait
  * is bounded by limit_us: when it runs out the kernel writes 106 into `status` (may be NULL)
  * and returns, and the context stays usable. */
 int lcg_peer_barrier(void* const* flags, int world, int rank, uint32_t epoch, int64_t limit_us,

@@ -80,15 +80,22 @@ def test_push_rejects_bad_arguments(lc):
 
 
 def test_barrier_alone_and_bounded(lc):
-    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    flags = torch.zeros(16, dtype=torch.int32, device="cuda")
     for epoch in (1, 2, 3):                      # a group of one passes at once
         lc.ops.peer_barrier([flags.data_ptr()], 0, epoch)
     torch.cuda.synchronize()
     assert int(flags[0]) == 3
+    for _ in range(2):                           # epoch 0: the kernel counts its own calls
+        lc.ops.peer_barrier([flags.data_ptr()], 0, 0)
+    torch.cuda.synchronize()
+    assert int(flags[8]) == 2 and int(flags[0]) == 2
+    flags.zero_()
+    for epoch in (1, 2, 3):
+        lc.ops.peer_barrier([flags.data_ptr()], 0, epoch)
     lc.ops.check_status()
     # a group of two whose other member never arrives: the wait runs out after 20 ms, the
     # kernel returns, the status word says which wait it was, and the context stays usable
-    other = torch.zeros(8, dtype=torch.int32, device="cuda")
+    other = torch.zeros(16, dtype=torch.int32, device="cuda")
     lc.ops.peer_barrier([flags.data_ptr(), other.data_ptr()], 0, 4, limit_us=20_000)
     torch.cuda.synchronize()
     assert int(other[0]) == 4                    # the arrival was announced

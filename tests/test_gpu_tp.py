@@ -62,12 +62,15 @@ def _worker(rank, world, port, ret):
         st.end()
         st.drain()
         streamed = max(rel(o.to(dev), out4[rank * rows:(rank + 1) * rows]) for o in got)
+        # the fused layer recorded into CUDA graphs (one per receive-region set), replayed
+        cap = tp.CapturedTensorParallel(fused, x)
+        captured = max(rel(cap().clone(), out4) for _ in range(3))
         full = Rank7MlpLayer(m, nw, wgu, wd, 1e-6)(x)
         dense = DenseMlpLayer(m, nw, wgu, wd, 1e-6, gemm="cublas")(x)
         ops.check_status()
         branch = lambda y: y.float() - x.float()
         ret[rank] = (rel(out, full), rel(branch(out), branch(dense)), rel(out2, out), rel(out3, out),
-                     rel(out4, out), rel(out5, ref5), streamed)
+                     rel(out4, out), rel(out5, ref5), streamed, captured)
     finally:
         dist.destroy_process_group()
 
@@ -81,7 +84,8 @@ def test_two_gpu_tensor_parallel_layer():
         mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
         assert len(ret) == 2
         for rank in range(2):
-            vs_full, branch_vs_dense, repeat, piped, fused, fused_next, streamed = ret[rank]
+            vs_full, branch_vs_dense, repeat, piped, fused, fused_next, streamed, captured = ret[rank]
+            assert captured < 4e-3, (rank, captured)
             assert streamed < 4e-3, (rank, streamed)
             assert piped < 4e-3, (rank, piped)
             assert fused < 4e-3, (rank, fused)                   # fp32 sum of the partials vs bf16

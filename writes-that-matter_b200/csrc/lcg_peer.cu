@@ -16,7 +16,7 @@ constexpr int kMaxWorld = 8;
 constexpr int kCodeBarrier = 106;
 
 struct BarrierArgs {
-  uint32_t* flags[kMaxWorld];   // flags[r]: rank r's flag array (kMaxWorld words), peer-mapped
+  uint32_t* flags[kMaxWorld];   // flags[r]: rank r's flag array (2 * kMaxWorld words), peer-mapped
   int32_t world, rank;
   uint32_t epoch;
   int32_t* status;
@@ -41,14 +41,20 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 // rank t has said the same here.  Epochs only grow, so a flag that is already ahead passes.
 // The wait is bounded: when it runs out the kernel records kCodeBarrier and returns.
 __global__ void k_peer_barrier(const BarrierArgs a) {
+  __shared__ uint32_t s_epoch;
   const int t = static_cast<int>(threadIdx.x);
+  // Epoch 0 in the arguments: count the calls on the device (word kMaxWorld of this rank's own
+  // array), so that the same launch can be replayed from a CUDA graph.
+  if (t == 0) s_epoch = a.epoch != 0u ? a.epoch : atomicAdd(a.flags[a.rank] + kMaxWorld, 1u) + 1u;
+  __syncthreads();
   if (t >= a.world) return;
+  const uint32_t epoch = s_epoch;
   __threadfence_system();
-  st_release_sys(a.flags[t] + a.rank, a.epoch);
+  st_release_sys(a.flags[t] + a.rank, epoch);
   const uint32_t* mine = a.flags[a.rank] + t;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
-  while (static_cast<int32_t>(ld_acquire_sys(mine) - a.epoch) < 0) {
+  while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
     __nanosleep(100);
     if ((++spins & 0x3fu) == 0 && globaltimer_ns() - t0 > a.limit_ns) {
       if (a.status != nullptr) atomicCAS(a.status, 0, kCodeBarrier);

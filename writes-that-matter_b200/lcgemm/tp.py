@@ -69,7 +69,7 @@ class PeerExchange:
 
     ``slots[b]``: ``(world, rows_per_owner, hidden)`` receive regions (two, used in turn);
     ``out``: the ``(tokens, hidden)`` layer output every owner writes its rows into;
-    ``flags``: eight words per rank for the barrier.  ``slot_ptrs[b][o]`` is the address, in
+    ``flags``: sixteen words per rank for the barrier (eight peers, the call counter).  ``slot_ptrs[b][o]`` is the address, in
     owner ``o``'s memory, of the region reserved for this rank.
     """
 
@@ -90,7 +90,7 @@ class PeerExchange:
         self.slots = [symm.empty((self.world, self.rows, hidden), dtype=torch.bfloat16, device=dev)
                       for _ in range(2)]
         self.out = symm.empty((tokens, hidden), dtype=torch.bfloat16, device=dev)
-        self.flags = symm.empty((8,), dtype=torch.int32, device=dev)
+        self.flags = symm.empty((16,), dtype=torch.int32, device=dev)
         self.flags.zero_()
         handles = [symm.rendezvous(t, group) for t in (*self.slots, self.out, self.flags)]
         mine = self.rank * self.rows * hidden * elem
@@ -98,16 +98,15 @@ class PeerExchange:
         self.out_ptrs = [int(p) for p in handles[2].buffer_ptrs]
         self.flag_ptrs = [int(p) for p in handles[3].buffer_ptrs]
         self._handles = handles
-        self.epoch = 0
         self.turn = 0
         torch.cuda.synchronize(dev)
         dist.barrier(group)          # every rank's flags are zero before the first peer barrier
 
     def barrier(self):
+        """Epochs are counted on the device, so a recorded layer call can be replayed."""
         from . import ops
 
-        self.epoch += 1
-        ops.peer_barrier(self.flag_ptrs, self.rank, self.epoch)
+        ops.peer_barrier(self.flag_ptrs, self.rank, 0)
 
 
 class TensorParallelMlp:
@@ -213,3 +212,33 @@ class TensorParallelMlp:
         return self.out
 
     __call__ = forward
+
+
+class CapturedTensorParallel:
+    """A fused tensor-parallel layer call as CUDA graphs: one replay per step.  The receive
+    regions are used in turn, so two recordings are kept (one per region set) and replayed
+    alternately; the barriers count their epochs on the device.  Every rank records and
+    replays in the same order."""
+
+    def __init__(self, layer: TensorParallelMlp, x: torch.Tensor, warmup: int = 2):
+        if layer.exchange is None:
+            raise ValueError("only the fused exchange (its own kernels, no library collective) is recorded")
+        self.layer, self.x = layer, x
+        side = torch.cuda.Stream(x.device)
+        side.wait_stream(torch.cuda.current_stream(x.device))
+        with torch.cuda.stream(side):
+            for _ in range(2 * warmup):
+                layer(x)
+        torch.cuda.current_stream(x.device).wait_stream(side)
+        torch.cuda.synchronize(x.device)
+        self.graphs = []
+        for _ in range(2):
+            self.graphs.append((layer.exchange.turn, torch.cuda.CUDAGraph()))
+            with torch.cuda.graph(self.graphs[-1][1]):
+                self.out = layer(x)
+        self.n = 0
+
+    def __call__(self) -> torch.Tensor:
+        self.graphs[self.n & 1][1].replay()
+        self.n += 1
+        return self.out
