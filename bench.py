@@ -26,8 +26,23 @@ and its result goes back to the host inside the timed region, the copies of neig
 steps overlapping the compute; the figure with copy, compute and copy one after the other
 is reported beside it (`serial_ms_per_step`).
 
---impl reference times the CPU evaluation of the same scheme (the oracle port of the
-reference's torch functions) on the host cores, on a bounded row sample of the workload.
+The N = 1 line also carries `sustained` (both layer arms run back to back for seconds, in
+alternating blocks, with the SM clock sampled per arm), `gemm_only` (the two GEMMs without
+their seams, rank-7 against dense tcgen05) and `tp1_same_config` (the tensor-parallel
+configuration on one GPU: the anchor of the strong-scaling curve); the N > 1 line carries
+`parity` (the fused exchange's output against the NCCL exchange and against a dense cuBLAS
+evaluation of a row sample, checked before anything is timed) and the same anchor.
+
+--impl reference times the reference's own CPU evaluation of the scheme on the host cores
+(its torch functions from the unmodified install under baseline/_ref when that is present,
+else the oracle port of them), on a bounded row sample of the workload, and evaluates the
+fp32 CPU configuration (2048 x 4096 x 4096) at its stated size.
+
+--rounds R runs the single-layer comparison as R matched rounds of fresh processes (one
+process per arm, order alternating) and reports the median and quartiles of the per-round
+speedups, the reference's protocol for making numbers comparable.
+--ref-kernels times the reference's own sm_100 kernels (from baseline/_ref, one GPU) beside
+this library's, or prints why they are unavailable.
 """
 from __future__ import annotations
 
@@ -183,8 +198,107 @@ def streamed_e2e_ms(layer, tokens, hidden, x_host, out_host, args, sync_all, gro
     return e0.elapsed_time(e1) / args.steps
 
 
+def _host_threads():
+    """Use every host core for the CPU arm (torchrun sets OMP_NUM_THREADS=1 for its workers)."""
+    n = os.cpu_count() or 1
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        pass
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
+def _import_reference():
+    """The reference's own torch functions for this path, from the unmodified install under
+    baseline/_ref (git-ignored; it travels with the working tree).  The reference package shares
+    its name with this repository's, so it is imported with only its own directory on the path;
+    callers of this function never touch this repository's package afterwards.  Returns a
+    namespace, or None when the install is absent or does not import."""
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "lcgemm" / "scheme.py").exists():
+        return None
+    saved_path, saved_mods = list(sys.path), {k: v for k, v in sys.modules.items()
+                                              if k == "lcgemm" or k.startswith("lcgemm.")}
+    for k in saved_mods:
+        del sys.modules[k]
+    ours = str(ROOT / "writes-that-matter_b200")
+    sys.path[:] = [str(ref)] + [q for q in sys.path if q != ours]
+    try:
+        import lcgemm.chain_gauge as gauge
+        import lcgemm.planes as planes
+        import lcgemm.scheme as scheme
+
+        if str(ref) not in str(Path(scheme.__file__).resolve()):
+            raise ImportError("lcgemm resolved outside baseline/_ref")
+        try:
+            from lcgemm.integrate.qwen_patch import _reference as functional
+        except Exception:
+            functional = None
+        return type("Ref", (), dict(scheme=scheme, planes=planes, gauge=gauge,
+                                    functional=staticmethod(functional) if functional else None))
+    except Exception:
+        for k in [k for k in sys.modules if k == "lcgemm" or k.startswith("lcgemm.")]:
+            del sys.modules[k]
+        sys.modules.update(saved_mods)
+        sys.path[:] = saved_path
+        return None
+
+
+def _ref_a_planes(x, sch):
+    """A planes by the reference's own pattern (lcgemm/chain_gauge.py:91-98 without SwiGLU or
+    gauge): fp32 signed sums over `Scheme.a_terms`, one rounding."""
+    m, k = x.shape
+    m2, k2 = m // sch.p, k // sch.q
+    out = torch.empty((sch.rank * m2, k2), dtype=x.dtype)
+    for r, terms in enumerate(sch.a_terms):
+        acc = torch.zeros(m2, k2, dtype=torch.float32)
+        for bi, bk, coeff in terms:
+            acc += float(coeff) * x[bi * m2:(bi + 1) * m2, bk * k2:(bk + 1) * k2].float()
+        out[r * m2:(r + 1) * m2] = acc.to(x.dtype)
+    return out
+
+
+def _ref_combine(a_pl, b_pl, sch, m, n, out_dtype):
+    """C[i][j] = sum_r c[r][i,j] * (A~_r @ B~_r^T) over `Scheme.c_terms` (lcgemm/scheme.py:160-163);
+    the products in fp32 from the (rounded) planes."""
+    m2, n2 = m // sch.p, n // sch.s
+    c = torch.zeros((m, n), dtype=torch.float32)
+    for r in range(sch.rank):
+        prod = a_pl[r * m2:(r + 1) * m2].float() @ b_pl[r * n2:(r + 1) * n2].float().T
+        for bi, bj, coeff in sch.c_terms[r]:
+            c[bi * m2:(bi + 1) * m2, bj * n2:(bj + 1) * n2] += float(coeff) * prod
+    return c.to(out_dtype)
+
+
+def reference_cpu_step(ref, tokens, hidden, inter):
+    """One MLP layer on the host by the reference's own functions: RMSNorm as its functional
+    layer does it (lcgemm/integrate/qwen_patch.py:49-52), its `prepare_b` / `prepare_down_b`
+    planes (untimed, offline in the reference too), the scheme evaluation composed from
+    `Scheme.a_terms` / `c_terms`, and its `chain_a_planes` for the SwiGLU seam."""
+    g = torch.Generator().manual_seed(0)
+    bf = torch.bfloat16
+    x = torch.randn((tokens, hidden), generator=g).to(bf)
+    nw = (torch.randn((hidden,), generator=g) * 0.01).to(bf)
+    wgu = (torch.randn((2 * inter, hidden), generator=g) * 0.02).to(bf)
+    wd = (torch.randn((hidden, inter), generator=g) * 0.02).to(bf)
+    gs, ds = ref.scheme.load("2x2_postsum_cse"), ref.scheme.load("2x2_locality_ordered")
+    gate_b = ref.planes.prepare_b(wgu, gs)
+    down_b = ref.gauge.prepare_down_b(wd, ds)
+
+    def step():
+        hf = x.float()
+        y = (hf * torch.rsqrt(hf.square().mean(-1, keepdim=True) + EPS) * (nw.float() + 1.0)).to(bf)
+        z = _ref_combine(_ref_a_planes(y, gs), gate_b, gs, tokens, 2 * inter, bf)
+        d_pl = ref.gauge.chain_a_planes(z, ds)
+        out = _ref_combine(d_pl, down_b, ds, tokens, hidden, bf)
+        return (x.float() + out.float()).to(bf)
+
+    return step, layer_flops(tokens, hidden, inter)
+
+
 def run_cpu_sample(tokens, hidden, inter, threads=None):
-    """The oracle's chained rank-7 layer on a row sample, host cores; returns (seconds, flops)."""
+    """The oracle's chained rank-7 layer on a row sample, host cores; returns (step, flops)."""
     from oracle import lc_oracle as O
 
     if threads:
@@ -213,10 +327,14 @@ def run_cpu_sample(tokens, hidden, inter, threads=None):
 
 
 def cpu_baseline(hidden, inter, reps=3):
+    """The oracle port on a row sample.  (Inside the GPU arm's process this repository's own
+    package is loaded, so the reference install, which shares its name, is left to
+    `--impl reference`.)"""
+    cores = _host_threads()
     step, flops = run_cpu_sample(CPU_SAMPLE_TOKENS, hidden, inter)
     step()
     best = min(_wall(step) for _ in range(reps))
-    return {"value": flops / best / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+    return {"value": flops / best / 1e12, "unit": "TFLOP/s", "cores": cores,
             "kind": "port",
             "sample": f"{CPU_SAMPLE_TOKENS} of the tokens, full hidden {hidden} / intermediate {inter}; "
                       f"oracle chained rank-7 layer (torch fp32 matmul on bf16-rounded planes), "
@@ -229,12 +347,53 @@ def _wall(fn):
     return time.perf_counter() - t0
 
 
+def cpu_config_fp32(ref, reps=5):
+    """The CPU configuration at its stated size: C = A @ B through the one-level rank-7 scheme in
+    fp32, A (2048 x 4096) ~ N(0, 1), B (4096 x 4096) ~ N(0, 0.02), seed 0, against dense A @ B."""
+    torch.manual_seed(0)
+    m, k, n = 2048, 4096, 4096
+    a = torch.randn(m, k)
+    b = torch.randn(k, n) * 0.02
+    w = b.T.contiguous()                       # weights are (N, K), K-major
+    dense = a @ b
+    t_dense = min(_wall(lambda: a @ b) for _ in range(reps))
+    out = {"shape": [m, k, n], "dtype": "f32", "seed": 0, "dense_ms": t_dense * 1e3, "schemes": {}}
+    for name in ("2x2_postsum_cse", "2x2_locality_ordered"):
+        if ref is not None:
+            sch = ref.scheme.load(name)
+            b_pl = ref.planes.prepare_b(w, sch)
+            fn = lambda: _ref_combine(_ref_a_planes(a, sch), b_pl, sch, m, n, torch.float32)
+        else:
+            from oracle import lc_oracle as O
+
+            tb = O.Tables(name)
+            fn = lambda: O.scheme_matmul(a, w, tb, mode="fp32")
+        c = fn()
+        best = min(_wall(fn) for _ in range(reps))
+        out["schemes"][name] = {
+            "rel_fro_vs_dense": float(((c - dense).norm() / dense.norm()).item()),
+            "max_abs_vs_dense": float((c - dense).abs().max().item()),
+            "ms": best * 1e3, "b_planes": "prepared untimed"}
+    return out
+
+
 # ------------------------------------------------------------------ reference arm
 def run_reference_arm(args, rank):
     if rank != 0:
         return
+    cores = _host_threads()
     cfg = SINGLE if args.gpus == 1 else TP
-    step, flops = run_cpu_sample(CPU_SAMPLE_TOKENS, cfg["hidden"], cfg["inter"])
+    ref = _import_reference()
+    if ref is not None:
+        kind = "reference"
+        step, flops = reference_cpu_step(ref, CPU_SAMPLE_TOKENS, cfg["hidden"], cfg["inter"])
+        what = ("the reference's own torch functions from the unmodified install under baseline/_ref "
+                "(Scheme tables, prepare_b, prepare_down_b, chain_a_planes; the scheme evaluation "
+                "composed from Scheme.a_terms / c_terms)")
+    else:
+        kind = "port"
+        step, flops = run_cpu_sample(CPU_SAMPLE_TOKENS, cfg["hidden"], cfg["inter"])
+        what = "oracle port of the reference's torch scheme evaluation (baseline/_ref absent)"
     for _ in range(min(args.warmup, 2)):
         step()
     steps = max(1, min(args.steps, 100))
@@ -242,17 +401,18 @@ def run_reference_arm(args, rank):
     ms = statistics.mean(times) * 1e3
     val = flops / (ms * 1e-3) / 1e12
     sample = (f"{CPU_SAMPLE_TOKENS}-token row sample of the {cfg['tokens']}-token layer per step, "
-              f"{steps} timed steps, oracle port of the reference's torch scheme "
-              f"evaluation on the host cores")
+              f"{steps} timed steps on the host cores; {what}")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": _workload_name(args.gpus), **cfg, "cpu_sample_tokens": CPU_SAMPLE_TOKENS},
-        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
-                         "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "what": "CPU evaluation of the path; the reference's sm_100 device kernels are timed by "
+                "`bench.py --ref-kernels` (one GPU)",
+        "cpu_config_fp32": cpu_config_fp32(ref) if args.gpus == 1 else None,
     }))
 
 
@@ -334,6 +494,7 @@ def bench_layer_arms(tokens, hidden, inter, steps, warmup, flush, device, with_p
     if with_parts:
         res["gate_up_ms"] = statistics.mean(e0.elapsed_time(e1) for e0, e1 in part_events)
     res["objects"] = (r7, x)
+    res["arms"] = arms
     return res
 
 
@@ -357,6 +518,22 @@ def run_ours(args, rank, world, device):
                                     flush, device, with_parts=True, graphs=args.graphs)
         clocks = cw.summary()
         r7, x = head.pop("objects")
+        head_arms = head.pop("arms")
+        sustained = None
+        if args.sustain_seconds > 0:
+            sustained = sustained_block(head_arms, args.sustain_seconds, torch.cuda.current_device())
+            sr, sd_, sc = (sustained[k] for k in ("rank7", "dense_tcgen05", "dense_cublas"))
+            sustained = {
+                "seconds_per_arm": args.sustain_seconds, "arms": sustained,
+                "how": "alternating blocks of ~0.4 s per arm, steps back to back (one step's operands exceed "
+                       "L2), SM clock sampled through NVML while each block runs",
+                "speedup_vs_dense_tcgen05_pct": (sd_["ms_per_step"] / sr["ms_per_step"] - 1) * 100,
+                "speedup_vs_cublas_pct": (sc["ms_per_step"] / sr["ms_per_step"] - 1) * 100,
+                "cycles_speedup_vs_dense_tcgen05_pct":
+                    (sd_["mcycles_per_step"] / sr["mcycles_per_step"] - 1) * 100 if sr["mcycles_per_step"] else None,
+                "rank7_effective_tflops": layer_flops(**cfg) / (sr["ms_per_step"] * 1e-3) / 1e12,
+            }
+        del head_arms
         ms = head["rank7"]["mean_ms"]
         flops = layer_flops(**cfg)
         value = flops / (ms * 1e-3) / 1e12
@@ -385,6 +562,10 @@ def run_ours(args, rank, world, device):
         by_tokens[str(cfg["tokens"])] = _arm_summary(head, flops)
         del r7, x
         torch.cuda.empty_cache()
+        sub_steps = max(5, args.steps // 2)
+        gemm_only = gemm_only_block(cfg["tokens"], cfg["hidden"], cfg["inter"], sub_steps, args.warmup, flush, device)
+        torch.cuda.empty_cache()
+        anchor = tp1_same_config(max(5, args.steps // 3), args.warmup, flush, device)
 
         gate_flops = 2.0 * cfg["tokens"] * cfg["hidden"] * 2 * cfg["inter"]
         gate_ms = head["gate_up_ms"]
@@ -395,6 +576,7 @@ def run_ours(args, rank, world, device):
             "peak_kind": f"{peak_kind} cuBLAS bf16 burst; sustained {peak_sustained}",
             "flops_per_launch": 0.875 * gate_flops, "effective_tflops": gate_flops / (gate_ms * 1e-3) / 1e12,
             "ms_per_launch": gate_ms, "traffic": GATE_UP_DRAM_TRAFFIC_BYTES,
+            "traffic_from": "profiles/k_gemm_gate_up_chain.md (one ncu capture of this launch; not re-measured by this run)",
         }
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
@@ -416,6 +598,7 @@ def run_ours(args, rank, world, device):
             "speedup_vs_dense_tcgen05_pct": by_tokens[str(cfg["tokens"])]["speedup_vs_dense_tcgen05_pct"],
             "speedup_vs_cublas_pct": by_tokens[str(cfg["tokens"])]["speedup_vs_cublas_pct"],
             "by_tokens": by_tokens, "roofline": roofline,
+            "sustained": sustained, "gemm_only": gemm_only, "tp1_same_config": anchor,
             "cpu_baseline": cpu_baseline(cfg["hidden"], cfg["inter"]),
         }
         print(json.dumps(line))
@@ -430,6 +613,20 @@ def run_ours(args, rank, world, device):
                                         inter_local=il, rank=rank)
     layer = TensorParallelMlp(cfg["tokens"], nw, wgu, wd, EPS, slabs=args.slabs,
                               fused=args.exchange == "peer")
+    parity = None
+    if args.exchange == "peer":
+        parity = tp_parity(layer, x, nw, wgu, wd, cfg, rank, world, device)
+        ops.check_status()
+        bad = [k for k, bound in parity["bounds"].items() if not parity[k] <= bound]
+        if bad or not parity["ranks_bit_identical"]:
+            if rank == 0:
+                print(json.dumps({"error": "tensor-parallel output failed its parity check", "parity": parity}))
+            raise SystemExit(3)
+    anchor = None
+    if args.tp1_anchor:
+        if rank == 0:
+            anchor = tp1_same_config(max(5, args.steps // 3), args.warmup, flush, device)
+        dist.barrier()
     launches0 = ops.launch_count()
     layer(x)
     launches = (ops.launch_count() - launches0) * args.steps
@@ -467,7 +664,6 @@ def run_ours(args, rank, world, device):
     ms, e2e_ms, e2e_serial_ms = t.tolist()
     if rank == 0:
         flops = layer_flops(**cfg)
-        per_rank_gate = 0.875 * 2.0 * cfg["tokens"] * cfg["hidden"] * 2 * il
         print(json.dumps({
             "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
@@ -489,8 +685,13 @@ def run_ours(args, rank, world, device):
             "roofline": {"bound": "tensor", "kernel": "whole step (per-rank rank-7 chain + exchange)",
                          "achieved": 0.875 * flops / (ms * 1e-3) / 1e12 / world, "peak": peak_burst,
                          "unit": "TFLOP/s per GPU", "frac": 0.875 * flops / (ms * 1e-3) / 1e12 / world / peak_burst,
-                         "peak_kind": f"{peak_kind} cuBLAS bf16 burst", "flops_per_launch": per_rank_gate,
+                         "peak_kind": f"{peak_kind} cuBLAS bf16 burst",
+                         "flops_per_launch": 0.875 * flops / world,
+                         "flops_per_launch_is": "executed FLOPs of one rank's whole step (gate_up + down), "
+                                                "the quantity `achieved` divides by the step time",
                          "traffic": None},
+            "parity": parity, "tp1_same_config": anchor,
+            "strong_scaling_vs_tp1": (anchor["ms_per_step"] / ms / world) if anchor else None,
         }))
 
 
@@ -503,6 +704,135 @@ def _arm_summary(res, flops):
             "dense_cublas_tflops": flops / (cb * 1e-3) / 1e12,
             "speedup_vs_dense_tcgen05_pct": (dt / r7 - 1.0) * 100.0,
             "speedup_vs_cublas_pct": (cb / r7 - 1.0) * 100.0}
+
+
+# --------------------------------------------- blocks beside the headline (same run)
+def sustained_block(arms, seconds, device_index, block_s=0.4):
+    """Every arm back to back for `seconds` in total, in alternating blocks of about `block_s`,
+    the SM clock sampled while each block runs.  No flush inside a block: one step's weights and
+    planes (1.5 GB) exceed L2.  Returns per arm the ms per step, the median SM clock of its own
+    blocks and their product (cycles per step, the clock-independent figure)."""
+    reps = {}
+    for name, fn in arms.items():
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            fn()
+        e1.record()
+        e1.synchronize()
+        reps[name] = max(5, int(block_s * 1e3 / (e0.elapsed_time(e1) / 5)))
+    acc = {name: {"ms": 0.0, "steps": 0, "mhz": []} for name in arms}
+    while min(a["ms"] for a in acc.values()) < seconds * 1e3:
+        for name, fn in arms.items():
+            with ClockWatch(device_index) as cw:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps[name]):
+                    fn()
+                e1.record()
+                e1.synchronize()
+            acc[name]["ms"] += e0.elapsed_time(e1)
+            acc[name]["steps"] += reps[name]
+            acc[name]["mhz"] += cw.samples
+    out = {}
+    for name, a in acc.items():
+        ms = a["ms"] / a["steps"]
+        mhz = statistics.median(a["mhz"]) if a["mhz"] else None
+        out[name] = {"ms_per_step": ms, "steps": a["steps"], "seconds": a["ms"] / 1e3, "sm_mhz_median": mhz,
+                     "mcycles_per_step": ms * mhz / 1e3 if mhz else None}
+    return out
+
+
+def gemm_only_block(tokens, hidden, inter, steps, warmup, flush, device):
+    """The two GEMMs of the layer without their seams: the rank-7 GEMM from operands that are
+    already in place (gate_up: A planes written beforehand; down: planes written beforehand, and
+    the form that builds its A operands inside the kernel from the activation matrix) against
+    the dense tcgen05 GEMM on the same inputs.  Cold L2, arms interleaved."""
+    from lcgemm import ops, scheme as S
+
+    bf = torch.bfloat16
+    x, _, wgu, wd = make_layer_tensors(tokens, hidden, inter, device)
+    cse, loc = S.load("2x2_postsum_cse"), S.load("2x2_locality_ordered")
+    s_act = torch.randn((tokens, inter), device=device).to(bf)
+    a_pl, d_pl = ops.a_planes(x, cse), ops.a_planes(s_act, loc)
+    bp_g, bp_d = ops.prepare_b(wgu, cse), ops.prepare_b(wd, loc)
+    z = torch.empty((tokens, 2 * inter), device=device, dtype=bf)
+    o = torch.empty((tokens, hidden), device=device, dtype=bf)
+    arms = {
+        "gate_up_rank7": lambda: ops.gemm_r7_planes(cse, a_pl, bp_g, tokens, 2 * inter, hidden, out=z),
+        "gate_up_dense_tcgen05": lambda: ops.gemm_dense(x, wgu, out=z),
+        "down_rank7_planes": lambda: ops.gemm_r7_planes(loc, d_pl, bp_d, tokens, hidden, inter, out=o),
+        "down_rank7_fused_a": lambda: ops.gemm_r7_fused(s_act, bp_d, hidden, loc, out=o),
+        "down_dense_tcgen05": lambda: ops.gemm_dense(s_act, wd, out=o),
+    }
+    for fn in arms.values():
+        for _ in range(warmup):
+            fn()
+    torch.cuda.synchronize()
+    times = {k: [] for k in arms}
+    for _ in range(steps):
+        for name, fn in arms.items():
+            times[name] += _event_times(fn, 1, 0, flush)
+    ops.check_status()
+    t = {k: statistics.mean(v) for k, v in times.items()}
+    return {"tokens": tokens, "ms": t, "note": "operands in place, no seams; hybrid schedule",
+            "gate_up_speedup_pct": (t["gate_up_dense_tcgen05"] / t["gate_up_rank7"] - 1) * 100,
+            "down_planes_speedup_pct": (t["down_dense_tcgen05"] / t["down_rank7_planes"] - 1) * 100,
+            "down_fused_a_speedup_pct": (t["down_dense_tcgen05"] / t["down_rank7_fused_a"] - 1) * 100}
+
+
+def tp1_same_config(steps, warmup, flush, device):
+    """The tensor-parallel configuration (8192 x 8192, intermediate 28672) on ONE GPU with the
+    single-GPU layer: the like-for-like anchor of the strong-scaling curve."""
+    from lcgemm import ops
+    from lcgemm.layer import CapturedLayer, Rank7MlpLayer
+
+    x, nw, wgu, wd = make_layer_tensors(TP["tokens"], TP["hidden"], TP["inter"], device)
+    layer = Rank7MlpLayer(TP["tokens"], nw, wgu, wd, EPS)
+    step = CapturedLayer(layer, x)
+    ms = statistics.mean(timed_steps(step, steps, warmup, flush, torch.cuda.synchronize))
+    ops.check_status()
+    del layer, step, x, nw, wgu, wd
+    torch.cuda.empty_cache()
+    return {"ms_per_step": ms, "tflops": layer_flops(**TP) / (ms * 1e-3) / 1e12, **TP}
+
+
+def tp_parity(fused_layer, x, nw, wgu, wd, cfg, rank, world, device):
+    """Checked before anything is timed: the fused exchange's output against the same layer
+    with one NCCL all-reduce, against a dense cuBLAS evaluation of a row sample (each rank its
+    shard's partial, summed over the ranks in fp32), and bit-equality of the ranks' copies."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from lcgemm.tp import TensorParallelMlp
+
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-30)).item()
+    out_f = fused_layer(x).clone()
+    ref = TensorParallelMlp(cfg["tokens"], nw, wgu, wd, EPS, fused=False)
+    out_n = ref(x).clone()
+    rows = torch.arange(0, cfg["tokens"], max(1, cfg["tokens"] // 256), device=device)[:256]
+    xs = x[rows]
+    h = xs.float()
+    y = (h * torch.rsqrt(h.square().mean(-1, keepdim=True) + EPS) * (nw.float() + 1.0)).to(torch.bfloat16)
+    gate_z, up_z = F.linear(y, wgu).chunk(2, dim=-1)
+    part = F.linear(F.silu(gate_z.float()).to(torch.bfloat16) * up_z, wd).float()
+    dist.all_reduce(part)
+    first = out_f.clone()
+    dist.broadcast(first, src=0)
+    same = torch.tensor([1 if torch.equal(first, out_f) else 0], device=device)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    res = torch.tensor([rel(out_f, out_n), rel(out_f.float() - x.float(), out_n.float() - x.float()),
+                        rel(out_f[rows].float() - xs.float(), part)], device=device, dtype=torch.float64)
+    dist.all_reduce(res, op=dist.ReduceOp.MAX)
+    del ref, out_n, first
+    torch.cuda.empty_cache()
+    vs_nccl, vs_nccl_branch, vs_dense_branch = res.tolist()
+    return {"vs_nccl_rel": vs_nccl, "vs_nccl_branch_rel": vs_nccl_branch, "vs_dense_rel": vs_dense_branch,
+            "ranks_bit_identical": bool(same.item()), "dense_rows": int(rows.numel()),
+            "bounds": {"vs_nccl_rel": 4e-3, "vs_nccl_branch_rel": 2e-2, "vs_dense_rel": 5e-2},
+            "note": "vs_nccl_rel on the whole output (residual included); the branch figures on "
+                    "out - x; max over ranks"}
 
 
 # ------------------------------------------------- kernel-level cases and the shape sweep
@@ -564,14 +894,18 @@ def run_case(args, device):
 
 
 def run_sweep(args, device):
-    """The bare-GEMM sweep: rank-7 GEMM (A planes + GEMM, B planes prepared offline) against
-    the dense tcgen05 GEMM and cuBLAS, odd shapes included, one JSON line per shape."""
+    """The bare-GEMM sweep: the rank-7 GEMM in both of its forms -- A planes written by a pass in
+    front of the GEMM (postsum-CSE scheme), and A operands formed inside the GEMM kernel
+    (locality-ordered scheme, where the shape allows it) -- against the dense tcgen05 GEMM and
+    cuBLAS, odd shapes included; B planes prepared offline.  One JSON line per shape; `rank7_ms`
+    is the form `lcgemm.ops.bare_gemm_form` dispatches that shape to."""
     from lcgemm import ops, scheme as S
 
     flush = torch.empty(FLUSH_BYTES, dtype=torch.int8, device=device)
+    kn_list = [kn for kn in SWEEP_KN if args.sweep_kn is None or f"{kn[0]}x{kn[1]}" in args.sweep_kn.split(",")]
     for m in (2048, 4096, 8192):
-        for k, n in SWEEP_KN:
-            sch = S.load("2x2_postsum_cse")
+        for k, n in kn_list:
+            sch, sch_f = S.load("2x2_postsum_cse"), S.load("2x2_locality_ordered")
             g = torch.Generator(device=device).manual_seed(m + k + n)
             a = torch.randn((m, k), generator=g, device=device).to(torch.bfloat16)
             w = (torch.randn((n, k), generator=g, device=device) * 0.02).to(torch.bfloat16)
@@ -581,10 +915,14 @@ def run_sweep(args, device):
             out = torch.empty((m, ld), device=device, dtype=torch.bfloat16)[:, :n]
             cb_out = torch.empty((m, n), device=device, dtype=torch.bfloat16)
             arms = {
-                "rank7": lambda: ops.gemm_r7(a, bp, n, sch, out=out, a_workspace=ws),
+                "rank7_planes": lambda: ops.gemm_r7(a, bp, n, sch, out=out, a_workspace=ws, fused=False),
                 "dense_tcgen05": lambda: ops.gemm_dense(a, w, out=out),
                 "dense_cublas": lambda: torch.matmul(a, w.t(), out=cb_out),
             }
+            fused_ok = ops.fused_a_supported(sch_f, m, n, k)
+            if fused_ok:
+                bp_f = ops.prepare_b(w, sch_f)
+                arms["rank7_fused"] = lambda: ops.gemm_r7_fused(a, bp_f, n, sch_f, out=out)
             for fn in arms.values():
                 for _ in range(args.warmup):
                     fn()
@@ -594,18 +932,26 @@ def run_sweep(args, device):
                 for name, fn in arms.items():
                     times[name] += _event_times(fn, 1, 0, flush)
             ops.check_status()
-            r7, dn, cb = (statistics.mean(times[x]) for x in ("rank7", "dense_tcgen05", "dense_cublas"))
+            t = {name: statistics.mean(v) for name, v in times.items()}
+            form = ops.bare_gemm_form(m, n, k)
+            r7 = t["rank7_fused"] if form[1] and fused_ok else t["rank7_planes"]
+            dn, cb = t["dense_tcgen05"], t["dense_cublas"]
             fl = 2.0 * m * n * k
             print(json.dumps({
-                "sweep": "bare_gemm", "M": m, "K": k, "N": n,
-                "schedule": "hybrid", "scheme": sch.name,
-                "rank7_ms": r7, "dense_tcgen05_ms": dn, "dense_cublas_ms": cb,
+                "sweep": "bare_gemm", "M": m, "K": k, "N": n, "schedule": "hybrid",
+                "dispatch": {"scheme": form[0], "fused_a": bool(form[1] and fused_ok)},
+                "rank7_ms": r7, "rank7_planes_ms": t["rank7_planes"], "rank7_fused_ms": t.get("rank7_fused"),
+                "dense_tcgen05_ms": dn, "dense_cublas_ms": cb,
                 "rank7_effective_tflops": fl / r7 / 1e9, "rank7_executed_tflops": 0.875 * fl / r7 / 1e9,
                 "dense_tcgen05_tflops": fl / dn / 1e9, "dense_cublas_tflops": fl / cb / 1e9,
                 "speedup_vs_dense_tcgen05_pct": (dn / r7 - 1) * 100, "speedup_vs_cublas_pct": (cb / r7 - 1) * 100,
-                "note": "rank7 time includes forming the A planes; L2 flushed between timed launches"}),
+                "fused_vs_dense_tcgen05_pct": (dn / t["rank7_fused"] - 1) * 100 if fused_ok else None,
+                "planes_vs_dense_tcgen05_pct": (dn / t["rank7_planes"] - 1) * 100,
+                "note": "rank7_planes time includes forming the A planes; L2 flushed between timed launches"}),
                 flush=True)
-            del a, w, bp, ws, out, cb_out
+            del a, w, bp, ws, out, cb_out, arms
+            if fused_ok:
+                del bp_f
             torch.cuda.empty_cache()
 
 
@@ -657,6 +1003,8 @@ def main():
                     help="time one kernel alone: gate_up | down | norm_planes | a_planes | dense_gate_up")
     ap.add_argument("--tokens", type=int, default=4096, help="token count for --case")
     ap.add_argument("--sweep", action="store_true", help="bare-GEMM shape sweep, odd shapes included")
+    ap.add_argument("--sweep-kn", default=None,
+                    help="restrict --sweep to these KxN pairs, comma separated (e.g. 17408x5120,16384x6144)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
@@ -667,6 +1015,10 @@ def main():
                     help="N > 1: how the ranks' partial outputs are combined: 'peer' = pushed from inside "
                          "the down GEMM over NVLink, then reduce + gather in this package's kernels; "
                          "'nccl' = one library all-reduce")
+    ap.add_argument("--sustain-seconds", type=float, default=2.0,
+                    help="N = 1: seconds per arm of the back-to-back `sustained` block (0 = skip)")
+    ap.add_argument("--no-tp1-anchor", dest="tp1_anchor", action="store_false",
+                    help="N > 1: skip timing the tensor-parallel configuration on rank 0 alone")
     ap.add_argument("--slabs", type=int, default=1,
                     help="N > 1: slabs of the down GEMM pipelined with the all-reduce (1 = no overlap)")
     args = ap.parse_args()

@@ -157,6 +157,25 @@ int lcg_gemm_r7(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,
                 int64_t M, int64_t N, int64_t K, int schedule, int cta_group,
                 int32_t* status, void* stream);
 
+/* Rank-7 C = A @ B^T straight from the activation matrix: the A operand of every product is
+ * formed inside the GEMM kernel, on its way into shared memory, so no A planes exist in global
+ * memory and the call needs no scratch.  Takes the place of the plane loads of the reference's
+ * mainloop (lcgemm/kernels/sm100.py:578-592) and of the plane-forming pass in front of it
+ * (lcgemm/planes.py:27-50 `apply_terms`): a product whose A row is a single block with
+ * coefficient +1 is loaded by TMA from that block; a product with two terms goes through eight
+ * producer warps (16-byte loads of both blocks, one packed bf16 add or subtract -- the fp32 sum
+ * rounded once -- swizzled stores into the operand stage).  The result equals lcg_a_planes +
+ * lcg_gemm_r7 with the same schedule bit for bit when the schedule is LCG_SCHEDULE_ALL_RANKS.
+ * Needs K % 128 == 0 and a scheme whose A rows have one or two +-1 terms
+ * (2x2_locality_ordered); anything else returns LCG_ERR_UNSUPPORTED_SHAPE / LCG_ERR_SCHEME and
+ * the caller uses the plane path.  a is (M, K) with lda % 8 == 0, 16-byte aligned. */
+int lcg_gemm_r7_fused(const lcg_scheme_t* scheme, const void* a, int64_t lda,
+                      const void* b_planes, int64_t ld_b, void* c, int64_t ldc,
+                      int64_t M, int64_t N, int64_t K, int schedule, int cta_group,
+                      int32_t* status, void* stream);
+/* 1 when lcg_gemm_r7_fused accepts this scheme and shape, else 0. */
+int lcg_gemm_r7_fused_supported(const lcg_scheme_t* scheme, int64_t M, int64_t N, int64_t K);
+
 /* lcg_gemm_r7 restricted to the tile rows [tile_row_begin, tile_row_end) of both block rows
  * (a tile row is 128 * cta_group rows of a block row: output rows i * M2 + [begin, end) * 256
  * for i = 0, 1 with the default pairing; tile_row_end < 0 means "to the last"), on at most

@@ -65,7 +65,7 @@ def test_rank7_gemm_against_oracle(lc, name, group, schedule, shape):
     sch, tb = lc.load(name), O.Tables(name)
     a, w = seeded((m, k), 5), seeded((n, k), 6, 0.02)
     bp = lc.planes.prepare_b(w, sch)
-    c = lc.ops.gemm_r7(a, bp, n, sch, schedule=schedule, cta_group=group)
+    c = lc.ops.gemm_r7(a, bp, n, sch, schedule=schedule, cta_group=group, fused=False)
     assert c.shape == (m, n)
     dense = a.double().cpu() @ w.double().cpu().T
     assert rel_fro(c, dense) <= TOL_R7_DENSE
@@ -79,7 +79,7 @@ def test_rank7_tiny_and_ragged_shapes(lc, shape):
     sch = lc.load("2x2_locality_ordered")
     a, w = seeded((m, k), 11), seeded((n, k), 12, 0.5)
     for schedule in (0, 1, 2):
-        c = lc.ops.gemm_r7(a, lc.planes.prepare_b(w, sch), n, sch, schedule=schedule)
+        c = lc.ops.gemm_r7(a, lc.planes.prepare_b(w, sch), n, sch, schedule=schedule, fused=False)
         assert c.shape == (m, n)
         want = a.double().cpu() @ w.double().cpu().T
         assert rel_fro(c, want) <= 1.5e-2
@@ -131,14 +131,14 @@ def test_full_size_properties(lc, name, schedule, shape):
     a = (torch.randn((m, k), device="cuda")).to(torch.bfloat16)
     w = (torch.randn((n, k), device="cuda") * 0.02).to(torch.bfloat16)
     bp = lc.planes.prepare_b(w, sch)
-    c = lc.ops.gemm_r7(a, bp, n, sch, schedule=schedule).clone()
+    c = lc.ops.gemm_r7(a, bp, n, sch, schedule=schedule, fused=False).clone()
     # (1) agrees with the dense tcgen05 kernel, which agrees with an fp32 product
     d = lc.ops.gemm_dense(a, w)
     assert rel_fro(c[:, ::7], d[:, ::7]) <= TOL_R7_DENSE
     exact = a[::5].float() @ w[::7].float().T                 # fp32 product of the same bf16 inputs
     assert rel_fro(d[::5, ::7], exact) <= TOL_DENSE
     # (2) scaling A by 2 scales C by 2 exactly (powers of two commute with every rounding)
-    c2 = lc.ops.gemm_r7((a.float() * 2).to(torch.bfloat16), bp, n, sch, schedule=schedule)
+    c2 = lc.ops.gemm_r7((a.float() * 2).to(torch.bfloat16), bp, n, sch, schedule=schedule, fused=False)
     if schedule == 0:
         assert torch.equal(c2.float(), c.float() * 2)
     else:                          # rank split: the order of the bf16 adds is not fixed
@@ -147,7 +147,7 @@ def test_full_size_properties(lc, name, schedule, shape):
     m2 = m // 2
     perm = torch.randperm(m2, device="cuda")
     full = torch.cat([perm, perm + m2])
-    cp = lc.ops.gemm_r7(a[full].contiguous(), bp, n, sch, schedule=schedule)
+    cp = lc.ops.gemm_r7(a[full].contiguous(), bp, n, sch, schedule=schedule, fused=False)
     if schedule == 0:
         assert torch.equal(cp, c[full])
     else:
@@ -156,7 +156,7 @@ def test_full_size_properties(lc, name, schedule, shape):
     az = a.clone()
     az[100:164] = 0
     az[m2 + 100:m2 + 164] = 0
-    cz = lc.ops.gemm_r7(az, bp, n, sch, schedule=schedule)
+    cz = lc.ops.gemm_r7(az, bp, n, sch, schedule=schedule, fused=False)
     assert bool((cz[100:164] == 0).all()) and bool((cz[m2 + 100:m2 + 164] == 0).all())
     # (5) column checksum: C @ 1 against A @ (W^T 1) in fp32
     ones = torch.ones(n, device="cuda")

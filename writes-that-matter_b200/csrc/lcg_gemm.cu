@@ -56,6 +56,8 @@ constexpr int kThreadsChain = 512;
 //   plain   (6 warps):  0 producer, 1 MMA, 2-5 epilogue
 //   chained (16 warps): 0 producer, 4 MMA (both scheduler 0), 1 2 3 8 epilogue,
 //                       5 6 7 9 10 11 13 14 plane warps (schedulers 1-3), 12 15 idle
+//   fused-A (16 warps): the chained layout with the plane warps' seats taken by the eight warps that
+//                       form the A operand tiles in shared memory
 template <bool kChain>
 struct Roles {
   static constexpr int kProducer = 0;
@@ -119,6 +121,21 @@ struct PushParams {
   int32_t m, n, m2, n2;
 };
 
+// Fused A-side producer: the GEMM reads the activation matrix itself and forms each product's
+// A operand tile (the signed sum of one or two of the four blocks of A) on its way into shared
+// memory, so no A planes exist in global memory.  Product r reads blocks blk[r][t] = i * 2 + k
+// with sign neg[r][t]; a product with a single +1 term is loaded by TMA straight into the operand
+// stage (simt[r] = 0), the others go through the eight producer warps' registers.
+struct FuseParams {
+  const __nv_bfloat16* a;     // (m, K) row-major, leading dimension lda
+  int64_t lda;
+  int32_t m, m2, k2;
+  int8_t nterm[kMaxRank];
+  int8_t simt[kMaxRank];
+  int8_t blk[kMaxRank][2];
+  int8_t neg[kMaxRank][2];
+};
+
 struct GemmParams {
   StepDesc steps[kMaxRank];        // whole-tile walk: chain plan, store-first scatter (or the dense step)
   StepDesc steps_split[kMaxRank];  // one product alone, reduce-add only
@@ -143,6 +160,7 @@ struct GemmParams {
   int32_t* status;
   ChainParams chain;
   PushParams push;
+  FuseParams fuse;
 };
 
 // Work unit -> (first step, tile row, tile column).  Tiles are walked in bands of
@@ -350,8 +368,23 @@ __device__ __forceinline__ void push_rows32(const PushParams& pp, int tn, int ro
 }
 
 // kMode: 0 plain GEMM; 1 chained (plane warps form SwiGLU + the consumer's planes behind each
-// tile); 2 push (the same warps copy each finished tile to the rank that owns its rows).
-constexpr int kModePlain = 0, kModePlanes = 1, kModePush = 2;
+// tile); 2 push (the same warps copy each finished tile to the rank that owns its rows);
+// 3 fused A (the same warps form the A operand tiles from the activation matrix's blocks).
+constexpr int kModePlain = 0, kModePlanes = 1, kModePush = 2, kModeFusedA = 3;
+// K blocks whose loads a fused-A producer thread keeps in flight in registers ahead of the block
+// it is writing into shared memory.
+constexpr int kFuseDepth = 2;
+
+__device__ __forceinline__ uint32_t bf16x2_add(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
 template <int kCtaGroup, int kMode, unsigned long long kPlaneCode = 0>
 __global__ void __launch_bounds__(kMode != kModePlain ? kThreadsChain : kThreadsPlain, 1)
 k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -388,8 +421,11 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
   const WaitCtl ctl{&misc_gen[1], p.status};
 
   if (threadIdx.x == 0) {
+    // A stage is full when the TMA producer's bytes have landed and, in the fused-A kernel, every
+    // A-producer warp of the group has written its share of the A tile.
+    constexpr uint32_t kFullArrivals = kMode == kModeFusedA ? 1u + 8u * kCtaGroup : 1u;
     for (uint32_t s = 0; s < T::kStages; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), kFullArrivals);
       mbar_init(empty_bar(s), 1);
     }
     for (uint32_t s = 0; s < 2; ++s) {
@@ -404,7 +440,8 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
     prefetch_tensormap(&tma_b);
     prefetch_tensormap(&tma_c.m[0]);
   }
-  constexpr bool kChain = kMode != kModePlain;
+  constexpr bool kChain = kMode != kModePlain;                              // the 16-warp layout
+  constexpr bool kHandoff = kMode == kModePlanes || kMode == kModePush;     // finished tiles go to the plane warps
   using R = Roles<kChain>;
   if (warp == R::kMma) {
     tmem_alloc<kCtaGroup>(misc, kTmemCols);
@@ -432,22 +469,31 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
         const UnitCoord uc = decode_unit(p, u);
         for (int s = uc.step0; s < uc.step0 + uc.nsteps; ++s) {
           const StepDesc& sd = uc.split ? p.steps_split[s] : p.steps[s];
-          const int a_row = sd.a_plane * p.a_plane_rows + uc.tm * T::kTileM +
-                            static_cast<int>(cta_rank) * kBM;
+          int a_row = sd.a_plane * p.a_plane_rows + uc.tm * T::kTileM +
+                      static_cast<int>(cta_rank) * kBM;
           const int b_row = sd.b_plane * p.b_plane_rows + uc.tn * kBN +
                             static_cast<int>(cta_rank) * T::kBRows;
           int kcol = uc.kb0 * kBK;
+          int a_col_off = 0;        // fused A: column of the block the single-term product reads
+          bool load_a = true;
+          if constexpr (kMode == kModeFusedA) {
+            const int blk = p.fuse.blk[sd.a_plane][0];
+            load_a = p.fuse.simt[sd.a_plane] == 0;
+            a_row = (blk >> 1) * p.fuse.m2 + uc.tm * T::kTileM + static_cast<int>(cta_rank) * kBM;
+            a_col_off = (blk & 1) * p.fuse.k2;
+          }
+          const uint32_t bytes = load_a ? T::kStageBytes : T::kBBytes;
           for (int kb = uc.kb0; kb < uc.kb1; ++kb, kcol += kBK) {
             mbar_wait(empty_bar(stage), wait_parity, ctl, kCodeProducer);
             const uint32_t sa = a_smem(stage);
             if constexpr (kCtaGroup == 1) {
-              mbar_arrive_expect_tx(full_bar(stage), T::kStageBytes);
-              tma_load_2d(sa, &tma_a, full_bar(stage), kcol, a_row);
+              mbar_arrive_expect_tx(full_bar(stage), bytes);
+              if (load_a) tma_load_2d(sa, &tma_a, full_bar(stage), kcol + a_col_off, a_row);
               tma_load_2d(sa + T::kABytes, &tma_b, full_bar(stage), kcol, b_row);
             } else {
-              if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * T::kStageBytes);
+              if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * bytes);
               const uint32_t bar = full_remote0 + 8u * stage;
-              tma_load_2d_pair(sa, &tma_a, bar, kcol, a_row);
+              if (load_a) tma_load_2d_pair(sa, &tma_a, bar, kcol + a_col_off, a_row);
               tma_load_2d_pair(sa + T::kABytes, &tma_b, bar, kcol, b_row);
             }
             if (++stage == T::kStages) {
@@ -576,7 +622,7 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
             mbar_arrive_cluster(acc_empty_remote + 8u * as);
         }
       }
-      if constexpr (kChain) {
+      if constexpr (kHandoff) {
         // Hand the unit to the plane warps.  A whole tile's C blocks are final once this CTA's
         // bulk copies have landed (single writer), so its plane job runs here, under the next
         // tile's MMAs.  A tail tile is written by several CTAs and is final only when the kernel
@@ -599,6 +645,152 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
     }
     if (issuer) bulk_wait_group<0>();
     __syncwarp();
+  } else if constexpr (kMode == kModeFusedA) {
+    if (plane_warp >= 0) {
+      // ------------------------------------------------------- A-operand producer warps
+      // 256 threads form the 128 x 64 A tile of every K block of every step this CTA walks:
+      // thread (rsub, vec) owns the 16-byte vector `vec` of rows rsub + 32 j (j = 0..3).  The
+      // blocks' vectors are loaded kFuseDepth K blocks ahead into registers, combined with one
+      // packed bf16 add or subtract (for two terms this is the fp32 sum rounded once: the exact sum
+      // of two bf16 values whose exponents differ by less than 16 fits fp32, and beyond that the
+      // smaller term cannot move the rounding of the larger), written with the 128-byte swizzle
+      // the MMA descriptors expect, fenced towards the async proxy, and the warp arrives on the
+      // stage's full barrier.  A step whose product reads a single block with coefficient +1 is
+      // loaded by the TMA producer instead; these warps then only wait and arrive.
+      const FuseParams& fp = p.fuse;
+      const int ptid = plane_warp * 32 + lane;
+      const int vec = ptid & 7;
+      const int rsub = ptid >> 3;
+      const uint32_t sw_off = static_cast<uint32_t>(rsub) * 128u +
+                              (static_cast<uint32_t>(vec ^ (rsub & 7)) << 4);
+      const uint32_t full_remote0 = kCtaGroup == 2 ? mapa_shared(full_bar(0), 0) : full_bar(0);
+      constexpr uint32_t kNone = 0xffffffffu;
+
+      // Walk of the (unit, step, K block) sequence, kFuseDepth items ahead of the writes.
+      int w_u = group_id, w_s = 0, w_s_end = 0, w_kb = 0, w_kb_end = 0;
+      bool w_valid = false, w_split = false;
+      UnitCoord w_uc = {};
+      const __nv_bfloat16* w_ptr[2] = {nullptr, nullptr};
+      // bit 0: the step goes through these warps; bits 1-2: its terms; bits 3-4: term negated;
+      // bit 8 + 4 t + j: vector j of term t lies past the last row of the matrix and reads as zero
+      uint32_t w_meta = 0;
+      auto w_begin_step = [&]() {
+        const StepDesc& sd = w_split ? p.steps_split[w_s] : p.steps[w_s];
+        const int r = sd.a_plane;
+        const int nterm = fp.nterm[r];
+        w_meta = (fp.simt[r] ? 1u : 0u) | (static_cast<uint32_t>(nterm) << 1) |
+                 (fp.neg[r][0] ? 8u : 0u) | (fp.neg[r][1] ? 16u : 0u);
+        const int row_in_block = w_uc.tm * T::kTileM + static_cast<int>(cta_rank) * kBM + rsub;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const int blk = fp.blk[r][t < nterm ? t : 0];
+          const int64_t grow = static_cast<int64_t>(blk >> 1) * fp.m2 + row_in_block;
+          w_ptr[t] = fp.a + grow * fp.lda + static_cast<int64_t>(blk & 1) * fp.k2 +
+                     static_cast<int64_t>(w_kb) * kBK + vec * 8;
+          // Rows past the end of the matrix must not be read.  (Rows past the end of a block
+          // row but inside the matrix feed accumulator rows that the clipped C maps never store.)
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (t < nterm && grow + 32 * j >= fp.m) w_meta |= 1u << (8 + 4 * t + j);
+        }
+      };
+      auto w_begin_unit = [&]() {
+        w_valid = w_u < p.num_units;
+        if (!w_valid) return;
+        w_uc = decode_unit(p, w_u);
+        w_split = w_uc.split != 0;
+        w_s = w_uc.step0;
+        w_s_end = w_uc.step0 + w_uc.nsteps;
+        w_kb = w_uc.kb0;
+        w_kb_end = w_uc.kb1;
+        w_begin_step();
+      };
+      auto w_advance = [&]() {
+        w_ptr[0] += kBK;
+        w_ptr[1] += kBK;
+        if (++w_kb < w_kb_end) return;
+        w_kb = w_uc.kb0;
+        if (++w_s < w_s_end) {
+          w_begin_step();
+          return;
+        }
+        w_u += num_groups;
+        w_begin_unit();
+      };
+      auto w_issue = [&](uint4 (&dst)[2][4]) -> uint32_t {
+        if (!w_valid) return kNone;
+        const uint32_t meta = w_meta;
+        if (meta & 1u) {
+          const int nterm = static_cast<int>((meta >> 1) & 3u);
+#pragma unroll
+          for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (t < nterm && ((meta >> (8 + 4 * t + j)) & 1u) == 0u)
+                dst[t][j] = __ldcg(reinterpret_cast<const uint4*>(w_ptr[t] + static_cast<int64_t>(32 * j) * fp.lda));
+              else
+                dst[t][j] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        w_advance();
+        return meta;
+      };
+
+      uint4 buf[kFuseDepth][2][4];
+      uint32_t meta[kFuseDepth];
+      w_begin_unit();
+#pragma unroll
+      for (int d = 0; d < kFuseDepth; ++d) meta[d] = w_issue(buf[d]);
+      uint32_t stage = 0, wait_parity = 1;
+      bool more = true;
+      while (more) {
+#pragma unroll
+        for (int d = 0; d < kFuseDepth; ++d) {
+          if (meta[d] == kNone) {
+            more = false;
+            break;
+          }
+          if (lane == 0) mbar_wait(empty_bar(stage), wait_parity, ctl, kCodePlane);
+          __syncwarp();
+          if (meta[d] & 1u) {
+            const uint32_t dst = a_smem(stage) + sw_off;
+            const bool two = ((meta[d] >> 1) & 3u) == 2u;
+            const bool neg0 = (meta[d] & 8u) != 0u, neg1 = (meta[d] & 16u) != 0u;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 x = buf[d][0][j];
+              const uint4 y = buf[d][1][j];
+              if (neg0) {      // -x (+- y): flip the signs, exact
+                x.x ^= 0x80008000u, x.y ^= 0x80008000u, x.z ^= 0x80008000u, x.w ^= 0x80008000u;
+              }
+              if (two) {
+                if (neg1) {
+                  x.x = bf16x2_sub(x.x, y.x), x.y = bf16x2_sub(x.y, y.y);
+                  x.z = bf16x2_sub(x.z, y.z), x.w = bf16x2_sub(x.w, y.w);
+                } else {
+                  x.x = bf16x2_add(x.x, y.x), x.y = bf16x2_add(x.y, y.y);
+                  x.z = bf16x2_add(x.z, y.z), x.w = bf16x2_add(x.w, y.w);
+                }
+              }
+              st_shared_v4(dst + static_cast<uint32_t>(j) * (32u * 128u), x.x, x.y, x.z, x.w);
+            }
+            fence_proxy_async_shared();
+          }
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kCtaGroup == 1)
+              mbar_arrive(full_bar(stage));
+            else
+              mbar_arrive_cluster(full_remote0 + 8u * stage);
+          }
+          if (++stage == T::kStages) {
+            stage = 0;
+            wait_parity ^= 1u;
+          }
+          meta[d] = w_issue(buf[d]);
+        }
+      }
+    }
   } else if constexpr (kChain) {
     if (plane_warp >= 0) {
     // ------------------------------------------------------------- plane warps
@@ -888,9 +1080,15 @@ void plan_units(int rank, int tiles, int groups, int k_blocks, int schedule, Gem
 int fill_r7(const lcg_scheme* scheme, const void* a_planes, int64_t ld_a, const void* b_planes,
             int64_t ld_b, void* c, int64_t ldc, int64_t M, int64_t N, const R7Geometry& g,
             int schedule, int cta_group, CUtensorMap* ma, CUtensorMap* mb, CMaps* mc,
-            GemmParams* p, int tm_begin = 0, int tm_end = -1, int max_groups = 0) {
+            GemmParams* p, int tm_begin = 0, int tm_end = -1, int max_groups = 0,
+            int64_t a_matrix_cols = 0) {
   const int tile_m = kBM * cta_group;
-  if (int e = make_map(ma, a_planes, g.k2p, scheme->rank * g.m2, ld_a, kBM, "A planes")) return e;
+  // a_matrix_cols > 0: `a_planes` is the (M, K) activation matrix itself (fused A producer).
+  if (a_matrix_cols > 0) {
+    if (int e = make_map(ma, a_planes, a_matrix_cols, M, ld_a, kBM, "A")) return e;
+  } else if (int e = make_map(ma, a_planes, g.k2p, scheme->rank * g.m2, ld_a, kBM, "A planes")) {
+    return e;
+  }
   if (int e = make_map(mb, b_planes, g.k2p, scheme->rank * g.n2, ld_b, kBN / cta_group, "B planes"))
     return e;
   for (int bi = 0; bi < 2; ++bi)
@@ -1010,6 +1208,81 @@ extern "C" int lcg_gemm_r7(const lcg_scheme_t* scheme, const void* a_planes, int
   auto st_ = static_cast<cudaStream_t>(stream);
   if (int e = zero_tail_tiles(p, c, ldc, M, N, g, cta_group, st_)) return e;
   return cta_group == 1 ? launch<1, kModePlain>(ma, mb, mc, p, st_) : launch<2, kModePlain>(ma, mb, mc, p, st_);
+}
+
+// Which blocks of A each product reads, for the fused A producer.  Fails for a table with more
+// than two terms in a row (the producer warps hold two blocks' vectors per K block).
+static int fill_fuse(const lcg_scheme* scheme, const void* a, int64_t lda, int64_t M, int64_t K,
+                     const R7Geometry& g, FuseParams* f) {
+  std::memset(f, 0, sizeof(*f));
+  f->a = static_cast<const __nv_bfloat16*>(a);
+  f->lda = lda;
+  f->m = static_cast<int32_t>(M);
+  f->m2 = static_cast<int32_t>(g.m2);
+  f->k2 = static_cast<int32_t>(K / 2);
+  for (int r = 0; r < scheme->rank; ++r) {
+    int n = 0;
+    for (int x = 0; x < 4; ++x) {
+      const int c = scheme->a[r][x];
+      if (c == 0) continue;
+      if ((c != 1 && c != -1) || n == 2)
+        return fail(LCG_ERR_SCHEME,
+                    "the fused A producer needs A-side rows with one or two +-1 terms; product %d of "
+                    "this scheme has more (use lcg_a_planes + lcg_gemm_r7)", r);
+      f->blk[r][n] = static_cast<int8_t>(x);
+      f->neg[r][n] = c < 0;
+      ++n;
+    }
+    if (n == 0) return fail(LCG_ERR_SCHEME, "product %d reads no block of A", r);
+    f->nterm[r] = static_cast<int8_t>(n);
+    f->simt[r] = !(n == 1 && !f->neg[r][0]);
+  }
+  return LCG_OK;
+}
+
+extern "C" int lcg_gemm_r7_fused_supported(const lcg_scheme_t* scheme, int64_t M, int64_t N, int64_t K) {
+  if (!scheme || M < 2 || N < 2 || K < 128 || K % 128 != 0) return 0;
+  for (int r = 0; r < scheme->rank; ++r) {
+    int n = 0;
+    for (int x = 0; x < 4; ++x) {
+      const int c = scheme->a[r][x];
+      if (c != 0 && c != 1 && c != -1) return 0;
+      n += c != 0;
+    }
+    if (n < 1 || n > 2) return 0;
+  }
+  return 1;
+}
+
+extern "C" int lcg_gemm_r7_fused(const lcg_scheme_t* scheme, const void* a, int64_t lda,
+                                 const void* b_planes, int64_t ld_b, void* c, int64_t ldc, int64_t M,
+                                 int64_t N, int64_t K, int schedule, int cta_group, int32_t* status,
+                                 void* stream) {
+  if (!scheme || !a || !b_planes || !c) return fail(LCG_ERR_BAD_ARG, "NULL operand");
+  if (schedule != LCG_SCHEDULE_ALL_RANKS && schedule != LCG_SCHEDULE_RANK_SPLIT &&
+      schedule != LCG_SCHEDULE_HYBRID)
+    return fail(LCG_ERR_BAD_ARG, "unknown schedule %d", schedule);
+  cta_group = resolve_group(cta_group);
+  if (cta_group != 1 && cta_group != 2) return fail(LCG_ERR_BAD_ARG, "cta_group must be 0, 1 or 2");
+  if (K < 128 || K % 128 != 0)
+    return fail(LCG_ERR_UNSUPPORTED_SHAPE,
+                "the fused A producer reads whole 64-column K blocks of each half of A: K %% 128 must "
+                "be 0, got K=%lld (use lcg_a_planes + lcg_gemm_r7)", (long long)K);
+  R7Geometry g;
+  if (int e = r7_geometry(M, N, K, &g)) return e;
+  if (ldc < N) return fail(LCG_ERR_BAD_ARG, "ldc below N");
+  if (lda < K || ld_b < g.k2p) return fail(LCG_ERR_BAD_ARG, "leading dimension below extent");
+  CUtensorMap ma, mb;
+  CMaps mc;
+  GemmParams p;
+  if (int e = fill_r7(scheme, a, lda, b_planes, ld_b, c, ldc, M, N, g, schedule, cta_group, &ma, &mb,
+                      &mc, &p, 0, -1, 0, K))
+    return e;
+  if (int e = fill_fuse(scheme, a, lda, M, K, g, &p.fuse)) return e;
+  p.status = status;
+  auto st_ = static_cast<cudaStream_t>(stream);
+  if (int e = zero_tail_tiles(p, c, ldc, M, N, g, cta_group, st_)) return e;
+  return cta_group == 1 ? launch<1, kModeFusedA>(ma, mb, mc, p, st_) : launch<2, kModeFusedA>(ma, mb, mc, p, st_);
 }
 
 extern "C" int lcg_gemm_r7_slab(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,

@@ -190,14 +190,74 @@ def gemm_r7_slab(scheme, a_pl, b_pl, m: int, n: int, k: int, out: torch.Tensor, 
                                  ptr(status_word(a_pl.device)), stream_ptr()))
 
 
+def fused_a_supported(scheme, m: int, n: int, k: int) -> bool:
+    """Whether the GEMM can form this scheme's A operands itself (no A planes in memory)."""
+    return bool(lib().lcg_gemm_r7_fused_supported(NativeScheme.of(scheme).handle, m, n, k))
+
+
+def gemm_r7_fused(a: torch.Tensor, b_pl: torch.Tensor, n: int, scheme, out: torch.Tensor | None = None,
+                  schedule: int = nat.SCHEDULE_HYBRID, cta_group: int = 0, zero_out: bool = True) -> torch.Tensor:
+    """Bare rank-7 GEMM straight from the activation matrix ``a (M, K)``: the A operand of every
+    product is formed inside the GEMM kernel (TMA for single-block products, producer warps for
+    two-block ones), so there is no plane-forming pass and no scratch."""
+    _need(a, "activation"), _need(b_pl, "B planes")
+    m, k = a.shape
+    if tuple(b_pl.shape) != b_plane_shape(scheme, n, k):
+        raise ValueError(f"B planes must be {b_plane_shape(scheme, n, k)}, got {tuple(b_pl.shape)}")
+    if out is None:
+        out = _padded_out(m, n, a.device)
+    _need(out, "out")
+    if tuple(out.shape) != (m, n):
+        raise ValueError(f"out must be ({m}, {n}), got {tuple(out.shape)}")
+    if schedule == nat.SCHEDULE_RANK_SPLIT and zero_out:
+        out.zero_()
+    check(lib().lcg_gemm_r7_fused(NativeScheme.of(scheme).handle, ptr(a), a.stride(0), ptr(b_pl),
+                                  b_pl.stride(0), ptr(out), out.stride(0), m, n, k, schedule, cta_group,
+                                  ptr(status_word(a.device)), stream_ptr()))
+    return out
+
+
 def gemm_r7(a: torch.Tensor, b_pl: torch.Tensor, n: int, scheme, out: torch.Tensor | None = None,
             a_workspace: torch.Tensor | None = None, schedule: int = nat.SCHEDULE_HYBRID,
-            cta_group: int = 0) -> torch.Tensor:
-    """Bare rank-7 GEMM: form the A planes of ``a (M, K)``, then multiply with prepared B planes."""
+            cta_group: int = 0, fused: bool | None = None) -> torch.Tensor:
+    """Bare rank-7 GEMM ``a (M, K) @ B^T`` with prepared B planes.
+
+    ``fused=True`` forms the A operands inside the GEMM kernel (:func:`gemm_r7_fused`);
+    ``fused=False`` writes the A planes to ``a_workspace`` first and multiplies from there;
+    ``None`` picks by shape (:func:`prefers_fused_a`)."""
     m, k = a.shape
+    if fused is None:
+        fused = prefers_fused_a(scheme, m, n, k)
+    if fused:
+        return gemm_r7_fused(a, b_pl, n, scheme, out=out, schedule=schedule, cta_group=cta_group)
     planes = a_planes(a, scheme, out=a_workspace)
     return gemm_r7_planes(scheme, planes, b_pl, m, n, k, out=out, schedule=schedule,
                           cta_group=cta_group)
+
+
+# Output-column tiles (256 wide, per block column) up to which the fused A producer is the
+# faster form of the bare GEMM.  An A plane tile written once is re-read by every column tile, so
+# the plane pass amortises over wide outputs; over narrow ones it costs more than the 1/8 of the
+# products the decomposition saves, while the fused producer's cost is per MMA step.
+FUSED_A_MAX_TILES_N = 16
+
+
+def bare_gemm_form(m: int, n: int, k: int):
+    """``(scheme name, fused)``: the form of the bare rank-7 GEMM an exact shape is dispatched
+    to.  Narrow outputs take the locality-ordered decomposition (one or two terms per A row)
+    with the A operands formed inside the kernel; wide ones take the postsum-CSE decomposition
+    (seven publications instead of twelve) on planes written by a pass in front."""
+    tiles_n = -(-((n + 1) // 2) // 256)
+    if k % 128 == 0 and k >= 128 and tiles_n <= FUSED_A_MAX_TILES_N:
+        return "2x2_locality_ordered", True
+    return "2x2_postsum_cse", False
+
+
+def prefers_fused_a(scheme, m: int, n: int, k: int) -> bool:
+    if not fused_a_supported(scheme, m, n, k):
+        return False
+    tiles_n = -(-((n + 1) // 2) // 256)
+    return tiles_n <= FUSED_A_MAX_TILES_N
 
 
 def gate_up_chain(scheme, plane_scheme, a_pl, b_pl, z, down_planes, preclear=None,
