@@ -955,23 +955,170 @@ def run_sweep(args, device):
             torch.cuda.empty_cache()
 
 
+def run_ref_kernels(args, device):
+    """The reference's own sm_100 kernels beside this library's, same GPU, same call: the fused
+    norm + A-plane kernel, the chained gate_up GEMM and the rank-split down GEMM of one layer at
+    `--tokens`.  The reference runs in a child process (baseline/ref_kernels.py: its package
+    shares this one's name) between two timings of this library's kernels; if it cannot import,
+    JIT-compile or run here, the line says so with the error text."""
+    import subprocess
+
+    from lcgemm import ops
+    from lcgemm.seams import build_chain
+
+    m, h, i = args.tokens, SINGLE["hidden"], SINGLE["inter"]
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.int8, device=device)
+    x, nw, wgu, wd = make_layer_tensors(m, h, i, device)
+    gate, down = build_chain((m, h, 2 * i), (m, i, h))
+    gate_bw, down_bw = gate.prepare_weight(wgu), down.prepare_weight(wd)
+    zero = torch.zeros_like(x)
+    a = gate.a_planes(x, zero, nw, EPS)
+    stages = {"norm_planes": lambda: gate.a_planes(x, zero, nw, EPS),
+              "gate_up": lambda: gate.gemm(a, gate_bw),
+              "down": lambda: down(prepared_w=down_bw)}
+
+    def ours():
+        out = {}
+        for name, fn in stages.items():
+            t = _event_times(fn, args.steps, args.warmup, flush)
+            out[name] = {"mean_us": statistics.mean(t) * 1e3, "median_us": statistics.median(t) * 1e3,
+                         "min_us": min(t) * 1e3}
+        ops.check_status()
+        return out
+
+    before = ours()
+    torch.cuda.synchronize()
+    child = ROOT / "baseline" / "ref_kernels.py"
+    ref = None
+    try:
+        proc = subprocess.run([sys.executable, str(child), str(m), str(args.steps), str(args.warmup)],
+                              capture_output=True, text=True, timeout=args.ref_timeout)
+        for ln in reversed(proc.stdout.strip().splitlines()):
+            if ln.startswith("{"):
+                ref = json.loads(ln)
+                break
+        if ref is None:
+            ref = {"unavailable": f"child exited {proc.returncode} without a result: "
+                                  + (proc.stderr.strip().splitlines() or ["(no output)"])[-1][-400:]}
+    except subprocess.TimeoutExpired:
+        ref = {"unavailable": f"child did not finish within {args.ref_timeout} s"}
+    after = ours()
+    print(json.dumps({"ref_kernels": True, "tokens": m, "hidden": h, "inter": i, "steps": args.steps,
+                      "warmup": args.warmup, "l2": "flushed between timed launches",
+                      "ours_before": before, "reference": ref, "ours_after": after,
+                      "describe": {"gate_up": gate.describe(), "down": down.describe()}}))
+
+
+def run_round_arm(args, device):
+    """One arm of one matched round, in a process of its own: median of `--steps` cold-L2 passes
+    of one layer (the reference's `cold_passes`, lcgemm/bench/common.py:116-127, with CUDA events
+    in place of the host clock)."""
+    from lcgemm import ops
+    from lcgemm.layer import CapturedLayer, DenseMlpLayer, Rank7MlpLayer
+
+    cfg = dict(SINGLE, tokens=args.tokens)
+    flush = torch.empty(FLUSH_BYTES, dtype=torch.int8, device=device)
+    x, nw, wgu, wd = make_layer_tensors(cfg["tokens"], cfg["hidden"], cfg["inter"], device)
+    if args.round_arm == "rank7":
+        layer = Rank7MlpLayer(cfg["tokens"], nw, wgu, wd, EPS)
+    else:
+        layer = DenseMlpLayer(cfg["tokens"], nw, wgu, wd, EPS,
+                              gemm="cublas" if args.round_arm == "dense_cublas" else "tcgen05")
+    step = CapturedLayer(layer, x)
+    with ClockWatch(torch.cuda.current_device()) as cw:
+        times = []
+        for _ in range(args.warmup):
+            step()
+        torch.cuda.synchronize()
+        for _ in range(args.steps):
+            time.sleep(0.02)
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3)
+    ops.check_status()
+    print("RESULT_JSON " + json.dumps({"arm": args.round_arm, "tokens": cfg["tokens"], "runs": len(times),
+                                       "median_us": statistics.median(times), "mean_us": statistics.mean(times),
+                                       "samples_us": times, "clocks": cw.summary()}))
+
+
+def _quantile(values, q):
+    """Linear interpolation at (n - 1) * q (lcgemm/bench/headline.py:27-35)."""
+    v = sorted(values)
+    pos = (len(v) - 1) * q
+    lo = int(pos)
+    hi = min(lo + 1, len(v) - 1)
+    return v[lo] + (v[hi] - v[lo]) * (pos - lo)
+
+
+def run_rounds(args):
+    """R matched rounds: every round runs each arm in a fresh process, the order alternating from
+    round to round (lcgemm/bench/headline.py:66-67); a round's speedup compares the arms' medians;
+    the result is the median and quartiles of the rounds' speedups, with a sign guard: every
+    round must fall on the side of zero the median does."""
+    import subprocess
+
+    arms = ("dense_tcgen05", "dense_cublas", "rank7")
+    rows = []
+    for r in range(1, args.rounds + 1):
+        order = arms if r % 2 else tuple(reversed(arms))
+        got = {}
+        for arm in order:
+            proc = subprocess.run([sys.executable, str(Path(__file__).resolve()), "--round-arm", arm,
+                                   "--tokens", str(args.tokens), "--steps", str(args.steps),
+                                   "--warmup", str(args.warmup)], capture_output=True, text=True)
+            line = next((ln for ln in proc.stdout.splitlines() if ln.startswith("RESULT_JSON ")), None)
+            if proc.returncode != 0 or line is None:
+                raise SystemExit(f"round {r} arm {arm} failed: {proc.stderr[-500:]}")
+            got[arm] = json.loads(line[len("RESULT_JSON "):])
+        rows.append({
+            "round": r, "order": list(order),
+            "median_us": {a: got[a]["median_us"] for a in arms},
+            "sm_mhz": {a: got[a]["clocks"]["sm_mhz"] for a in arms},
+            "speedup_vs_dense_tcgen05_pct": 100 * (got["dense_tcgen05"]["median_us"] / got["rank7"]["median_us"] - 1),
+            "speedup_vs_cublas_pct": 100 * (got["dense_cublas"]["median_us"] / got["rank7"]["median_us"] - 1)})
+
+    def dist(key):
+        vals = [row[key] for row in rows]
+        med = _quantile(vals, 0.5)
+        return {"n": len(vals), "q1": _quantile(vals, 0.25), "median": med, "q3": _quantile(vals, 0.75),
+                "values": vals, "sign_consistent": all((v > 0) == (med > 0) for v in vals)}
+
+    print(json.dumps({"rounds": args.rounds, "tokens": args.tokens, "runs_per_arm": args.steps,
+                      "protocol": "fresh process per arm, arm order alternating by round, cold L2 before every "
+                                  "pass, one CUDA graph replay per pass, median of passes per arm, median of "
+                                  "rounds (quartiles beside it)",
+                      "speedup_vs_dense_tcgen05_pct": dist("speedup_vs_dense_tcgen05_pct"),
+                      "speedup_vs_cublas_pct": dist("speedup_vs_cublas_pct"), "rows": rows}))
+
+
 def run_model(args, device):
     """The end-to-end configuration: batch-1 prefill of a random-init 64-layer dense decoder, stock MLP vs
-    rank-7 MLP, on seeded uniform-random prompts of 2048 / 4096 / 8192 tokens."""
+    rank-7 MLP, on seeded uniform-random prompts of 2048 / 4096 / 8192 tokens.  Times come from the
+    first prompt of a length; agreement (equal top-1, tie-aware top-20 count, final hidden state)
+    is taken over `--prompts` seeded prompts per length and reported as rates, for the rank-7 arm,
+    for its bit-reproducible all-ranks form, and for the calibration pair `eager` vs `stock` (two
+    implementations of the same stock layer that differ only in where SwiGLU rounds)."""
     from lcgemm import ops
     from lcgemm.model import DecoderConfig, RandomInitDecoder, compare_arms
 
     cfg = DecoderConfig(layers=args.layers)
     model = RandomInitDecoder(cfg, device)
     flush = torch.empty(FLUSH_BYTES, dtype=torch.int8, device=device)
-    for tokens in (2048, 4096, 8192):
+    lengths = [int(t) for t in args.model_tokens.split(",")]
+    for tokens in lengths:
         info = model.install(tokens)
-        ids = torch.randint(0, cfg.vocab, (tokens,), generator=torch.Generator().manual_seed(tokens)).to(device)
-        outs, times = {}, {"stock": [], "rank7": [], "dense": []}
+        prompts = [torch.randint(0, cfg.vocab, (tokens,),
+                                 generator=torch.Generator().manual_seed(tokens + 7919 * j)).to(device)
+                   for j in range(args.prompts)]
+        ids = prompts[0]
+        times = {"stock": [], "rank7": [], "dense": []}
         for arm in times:
             for _ in range(max(1, args.warmup - 2)):
-                outs[arm] = model.prefill(ids, arm=arm)
-        outs["eager"] = model.prefill(ids, arm="eager")
+                model.prefill(ids, arm=arm)
         torch.cuda.synchronize()
         before = dict(model.calls)
         for _ in range(args.steps):
@@ -980,7 +1127,29 @@ def run_model(args, device):
         ops.check_status()
         fused = model.calls["fused"] - before["fused"]
         st, r7, dn = (statistics.median(times[a]) for a in ("stock", "rank7", "dense"))
-        cmp = lambda a, b: compare_arms(outs[a][0], outs[b][0], outs[a][1], outs[b][1])
+        pairs = {"rank7": [], "rank7_allranks": [], "eager": [], "dense": []}
+        repeat_equal = []
+        for ids_j in prompts:
+            ref = model.prefill(ids_j, arm="stock")
+            for arm in pairs:
+                got = model.prefill(ids_j, arm=arm)
+                pairs[arm].append(compare_arms(ref[0], got[0], ref[1], got[1]))
+                if arm == "rank7_allranks":
+                    again = model.prefill(ids_j, arm=arm)
+                    repeat_equal.append(bool(torch.equal(got[0], again[0]) and torch.equal(got[1], again[1])))
+        ops.check_status()
+
+        def rates(rows):
+            n = len(rows)
+            return {"prompts": n, "top1_equal_rate": sum(r["top1_equal"] for r in rows) / n,
+                    "tie_aware_top20_min": min(r["tie_aware_top20"] for r in rows),
+                    "tie_aware_top20_mean": sum(r["tie_aware_top20"] for r in rows) / n,
+                    "passes_gate_rate": sum(r["top1_equal"] and r["tie_aware_top20"] >= 19 for r in rows) / n,
+                    "hidden_rel_fro_mean": sum(r["hidden_rel_fro"] for r in rows) / n,
+                    "max_abs_logit_diff_max": max(r["max_abs_logit_diff"] for r in rows),
+                    "top1_gap_of_stock_median": statistics.median(r["top1_gap"] for r in rows),
+                    "logit_std": rows[0]["logit_std"]}
+
         print(json.dumps({
             "model": "random-init dense decoder", "layers": cfg.layers, "hidden": cfg.hidden,
             "inter": cfg.inter, "heads": [cfg.q_heads, cfg.kv_heads, cfg.head_dim], "vocab": cfg.vocab,
@@ -988,9 +1157,12 @@ def run_model(args, device):
             "speedup_pct": (st / r7 - 1.0) * 100.0, "speedup_vs_dense_tcgen05_pct": (dn / r7 - 1.0) * 100.0,
             "fused_calls": fused,
             "expected_fused_calls": args.steps * cfg.layers, "planes_gib": info["planes_gib"],
-            "agreement_rank7_vs_stock": cmp("stock", "rank7"),
-            "agreement_dense_tcgen05_vs_stock": cmp("stock", "dense"),
-            "agreement_eager_vs_stock": cmp("stock", "eager"),
+            "gate": "equal top-1 and >= 19 of 20 tie-aware (lcgemm/bench/headline.py:195-200)",
+            "agreement_rank7_vs_stock": rates(pairs["rank7"]),
+            "agreement_rank7_allranks_vs_stock": rates(pairs["rank7_allranks"]),
+            "agreement_dense_tcgen05_vs_stock": rates(pairs["dense"]),
+            "agreement_eager_vs_stock": rates(pairs["eager"]),
+            "rank7_allranks_repeat_bit_equal_rate": sum(repeat_equal) / len(repeat_equal),
             "data": "synthetic: random-init weights (seed 0), uniform-random token ids"}), flush=True)
 
 
@@ -999,6 +1171,8 @@ def main():
     ap.add_argument("--model", action="store_true",
                     help="end-to-end prefill of the random-init decoder")
     ap.add_argument("--layers", type=int, default=64, help="decoder layers for --model")
+    ap.add_argument("--prompts", type=int, default=8, help="seeded prompts per length for --model's agreement rates")
+    ap.add_argument("--model-tokens", default="2048,4096,8192", help="prompt lengths for --model")
     ap.add_argument("--case", default=None,
                     help="time one kernel alone: gate_up | down | norm_planes | a_planes | dense_gate_up")
     ap.add_argument("--tokens", type=int, default=4096, help="token count for --case")
@@ -1015,6 +1189,13 @@ def main():
                     help="N > 1: how the ranks' partial outputs are combined: 'peer' = pushed from inside "
                          "the down GEMM over NVLink, then reduce + gather in this package's kernels; "
                          "'nccl' = one library all-reduce")
+    ap.add_argument("--ref-kernels", action="store_true",
+                    help="time the reference's own sm_100 kernels (baseline/_ref) beside this library's, one GPU")
+    ap.add_argument("--ref-timeout", type=int, default=420, help="seconds the --ref-kernels child may take")
+    ap.add_argument("--rounds", type=int, default=0,
+                    help="matched rounds of fresh processes, one per arm (single layer at --tokens)")
+    ap.add_argument("--round-arm", default=None, choices=("rank7", "dense_tcgen05", "dense_cublas"),
+                    help="(used by --rounds) run one arm in this process and print its RESULT_JSON line")
     ap.add_argument("--sustain-seconds", type=float, default=2.0,
                     help="N = 1: seconds per arm of the back-to-back `sustained` block (0 = skip)")
     ap.add_argument("--no-tp1-anchor", dest="tp1_anchor", action="store_false",
@@ -1030,15 +1211,23 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank)
         return
+    if args.rounds > 0:
+        if world != 1:
+            raise SystemExit("--rounds runs on one GPU")
+        return run_rounds(args)
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch under torchrun); got {world}")
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the rank-7 path has no CPU implementation")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    if args.case or args.sweep or args.model:
+    if args.case or args.sweep or args.model or args.ref_kernels or args.round_arm:
         if world != 1:
-            raise SystemExit("--case / --sweep / --model run on one GPU")
+            raise SystemExit("--case / --sweep / --model / --ref-kernels / --rounds run on one GPU")
+        if args.ref_kernels:
+            return run_ref_kernels(args, device)
+        if args.round_arm:
+            return run_round_arm(args, device)
         if args.model:
             return run_model(args, device)
         return run_case(args, device) if args.case else run_sweep(args, device)

@@ -255,8 +255,14 @@ int lcg_reduce_gather(const void* slots, const void* h, int64_t ld_h, void* cons
  *
  * The A planes -- the scratch lcg_a_planes + lcg_gemm_r7 keep in a caller-owned buffer
  * -- live in a fixed array of lcg_static_scratch_bytes() (32 MiB) of device memory
- * inside the library; every GPU that loads the library holds it until the process
- * exits.  The call allocates and frees nothing.  Limits and rules:
+ * inside the library.  A GPU takes that memory when the array's address is first
+ * resolved on it -- by lcg_static_reserve() or by the first lcg_gemm_r7_static call
+ * there (CUDA loads modules lazily) -- and holds it until the process exits; that first
+ * resolution may fail for lack of memory or synchronise the device, so a host that sizes
+ * its pool from the free memory, or that must not stall later, calls
+ * lcg_static_reserve() on every device at start-up, before it sizes the pool (or runs
+ * with CUDA_MODULE_LOADING=EAGER).  After that the call allocates and frees nothing.
+ * Limits and rules:
  *   - rank * ceil(M/2) * round_up(ceil(K/2), 64) * 2 bytes must fit in the array
  *     (e.g. M = 2048, K = 4096); larger shapes return LCG_ERR_UNSUPPORTED_SHAPE;
  *   - the first call on a device resolves the array's address (once per device, with
@@ -271,6 +277,9 @@ int lcg_gemm_r7_static(const lcg_scheme_t* scheme, const void* a, int64_t lda,
                        int64_t M, int64_t N, int64_t K, int schedule, int cta_group,
                        int32_t* status, void* stream);
 int64_t lcg_static_scratch_bytes(void);
+/* Resolve the static scratch of the current device now (takes its memory there; see above).
+ * Idempotent.  No counterpart in the reference. */
+int lcg_static_reserve(void);
 
 /* ---- dense-arm seams (the stock layer the rank-7 path is compared with) -- */
 

@@ -47,8 +47,14 @@ def _worker(rank, world, port, ret):
         fused = tp.TensorParallelMlp(m, nw, gu_shard, d_shard, 1e-6, fused=True)
         out4 = fused(x).clone()                       # exchange in this package's own kernels
         out4 = fused(x).clone()
-        out5 = fused(out4.clone(), x).clone()         # a second layer call on the other slot set
+        # a second layer object on the SAME symmetric buffers (layers of a model share one exchange)
+        fused_b = tp.TensorParallelMlp(m, nw, gu_shard, d_shard, 1e-6, fused=True, exchange=fused.exchange)
+        out5 = fused_b(out4.clone(), x).clone()       # a second layer call on the other slot set
         ref5 = layer(out4.clone(), x).clone()
+        # every rank must hold the same bits: the owners sum in rank order and store one result
+        theirs = [torch.empty_like(out4) for _ in range(world)]
+        dist.all_gather(theirs, out4)
+        ranks_equal = all(torch.equal(t, out4) for t in theirs)
         rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
         # host-to-host streaming: every rank feeds its rows of the batch and gets its rows back
         from lcgemm.streaming import HostStreamedLayer
@@ -65,12 +71,14 @@ def _worker(rank, world, port, ret):
         # the fused layer recorded into CUDA graphs (one per receive-region set), replayed
         cap = tp.CapturedTensorParallel(fused, x)
         captured = max(rel(cap().clone(), out4) for _ in range(3))
+        captured_branch = max(rel(cap().clone().float() - x.float(), out4.float() - x.float()) for _ in range(2))
         full = Rank7MlpLayer(m, nw, wgu, wd, 1e-6)(x)
         dense = DenseMlpLayer(m, nw, wgu, wd, 1e-6, gemm="cublas")(x)
         ops.check_status()
         branch = lambda y: y.float() - x.float()
         ret[rank] = (rel(out, full), rel(branch(out), branch(dense)), rel(out2, out), rel(out3, out),
-                     rel(out4, out), rel(out5, ref5), streamed, captured)
+                     rel(out4, out), rel(out5, ref5), streamed, captured,
+                     rel(branch(out4), branch(out)), ranks_equal, captured_branch)
     finally:
         dist.destroy_process_group()
 
@@ -84,7 +92,15 @@ def test_two_gpu_tensor_parallel_layer():
         mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
         assert len(ret) == 2
         for rank in range(2):
-            vs_full, branch_vs_dense, repeat, piped, fused, fused_next, streamed, captured = ret[rank]
+            (vs_full, branch_vs_dense, repeat, piped, fused, fused_next, streamed, captured,
+             fused_branch, ranks_equal, captured_branch) = ret[rank]
+            # the MLP branch (output minus residual) is ~9 % of the output here, so the bounds on
+            # the whole output are loose on the branch; these are on the branch itself
+            assert fused_branch < 1.5e-2, (rank, fused_branch)   # fp32 sum of partials vs bf16 all-reduce
+            assert ranks_equal, rank                              # all ranks hold identical bits
+            # graph replay vs eager launches of the same kernels: the split tail of the push GEMM adds
+            # into C in an order the hardware picks, so equal up to that, not bit for bit
+            assert captured_branch < 1.0e-2, (rank, captured_branch)
             assert captured < 4e-3, (rank, captured)
             assert streamed < 4e-3, (rank, streamed)
             assert piped < 4e-3, (rank, piped)
@@ -93,4 +109,4 @@ def test_two_gpu_tensor_parallel_layer():
             assert vs_full < 4e-3, (rank, vs_full)               # residual-dominated output
             assert branch_vs_dense < 5e-2, (rank, branch_vs_dense)
             assert repeat < 4e-3, (rank, repeat)
-        assert ret[0] == pytest.approx(ret[1], rel=0.5, abs=1e-3)
+        assert ret[0][:9] == pytest.approx(ret[1][:9], rel=0.5, abs=1e-3)

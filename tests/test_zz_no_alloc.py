@@ -38,12 +38,16 @@ def _run_pair(lib, nat, scheme, m, n, k, seed, schedule):
                               m, n, k, schedule, 0, status.data_ptr(), stream))
     # new path: scratch inside the library
     got = torch.zeros((m, ld), dtype=torch.bfloat16, device="cuda")
+    nat.check(lib.lcg_static_reserve())           # the array takes its memory here, once per device
+    torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    free_before, _ = torch.cuda.mem_get_info()    # the driver's figure: sees any cudaMalloc, not only torch's
     nat.check(lib.lcg_gemm_r7_static(handle, a.data_ptr(), a.stride(0), bp.data_ptr(), k2p,
                                      got.data_ptr(), ld, m, n, k, schedule, 0, status.data_ptr(),
                                      stream))
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == before
+    assert torch.cuda.mem_get_info()[0] >= free_before
     assert status.tolist() == [0, 0, 0, 0]
     return got[:, :n], want[:, :n], a, w
 
@@ -62,10 +66,32 @@ def test_static_scratch_matches_caller_owned_scratch_twice():
         exact = a.double().cpu() @ w.double().cpu().T
         rel = ((got.double().cpu() - exact).norm() / exact.norm()).item()
         assert rel <= 1.0e-2
-    # rank split: the bf16 adds land in hardware order, so compare within the suite's tolerance
-    got, want, _, _ = _run_pair(lib, nat, sch, 512, 1024, 256, 3, nat.SCHEDULE_RANK_SPLIT)
-    rel = ((got.float() - want.float()).norm() / want.float().norm()).item()
-    assert rel <= 8.0e-3
+    # rank split and hybrid: the bf16 adds land in hardware order, so compare within the suite's tolerance
+    for schedule, shape in ((nat.SCHEDULE_RANK_SPLIT, (512, 1024, 256)), (nat.SCHEDULE_HYBRID, (1280, 9000, 128))):
+        got, want, _, _ = _run_pair(lib, nat, sch, *shape, 3, schedule)
+        rel = ((got.float() - want.float()).norm() / want.float().norm()).item()
+        assert rel <= 8.0e-3
+
+
+def test_static_scratch_boundary():
+    """A shape whose planes need exactly the 32 MiB passes the size check, one more row pair
+    does not.  Both calls name a leading dimension below K, which the host refuses before it
+    launches anything, so the first call gets past the size check and stops there."""
+    from lcgemm import _native as nat
+    from lcgemm import scheme as S
+
+    lib = nat.lib()
+    handle = nat.NativeScheme.of(S.load("2x2_locality_ordered")).handle
+    x = torch.zeros(8, dtype=torch.bfloat16, device="cuda")
+    m, k = 2048, 4096                       # 7 * 1024 * 2048 * 2 bytes = 32 MiB
+    assert 7 * (m // 2) * (k // 2) * 2 == lib.lcg_static_scratch_bytes()
+    bad_lda = 8
+    code = lib.lcg_gemm_r7_static(handle, x.data_ptr(), bad_lda, x.data_ptr(), k // 2, x.data_ptr(), 8,
+                                  m, 16, k, 0, 0, None, None)
+    assert code == nat.ERR_BAD_ARG and b"scratch" not in lib.lcg_last_error()
+    code = lib.lcg_gemm_r7_static(handle, x.data_ptr(), bad_lda, x.data_ptr(), k // 2, x.data_ptr(), 8,
+                                  m + 2, 16, k, 0, 0, None, None)
+    assert code == nat.ERR_UNSUPPORTED_SHAPE and b"scratch" in lib.lcg_last_error()
 
 
 def test_static_scratch_rejects_oversized_shapes():

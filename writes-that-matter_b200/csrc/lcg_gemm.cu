@@ -134,6 +134,7 @@ struct FuseParams {
   int8_t simt[kMaxRank];
   int8_t blk[kMaxRank][2];
   int8_t neg[kMaxRank][2];
+  int32_t debug;
 };
 
 struct GemmParams {
@@ -720,8 +721,8 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
       auto w_issue = [&](uint4 (&dst)[2][4]) -> uint32_t {
         if (!w_valid) return kNone;
         const uint32_t meta = w_meta;
-        if (meta & 1u) {
-          const int nterm = static_cast<int>((meta >> 1) & 3u);
+        if ((meta & 1u) && fp.debug != 1) {
+          const int nterm = fp.debug == 3 ? 1 : static_cast<int>((meta >> 1) & 3u);
 #pragma unroll
           for (int t = 0; t < 2; ++t)
 #pragma unroll
@@ -1237,6 +1238,7 @@ static int fill_fuse(const lcg_scheme* scheme, const void* a, int64_t lda, int64
     f->nterm[r] = static_cast<int8_t>(n);
     f->simt[r] = !(n == 1 && !f->neg[r][0]);
   }
+  if (const char* dbg = getenv("LCG_FUSE_DEBUG")) f->debug = atoi(dbg);
   return LCG_OK;
 }
 

@@ -7,8 +7,12 @@
 // memory is free at start-up leaves nothing for a plugin to cudaMalloc later, and a
 // serving thread may be forbidden to allocate at all because cudaMalloc synchronises
 // the device.  For them the scratch lives in this translation unit as a fixed array
-// in device memory, reserved when the library is loaded on a GPU and held until the
-// process exits.
+// in device memory.  With CUDA's lazy module loading (the default since CUDA 12.2) the
+// array takes its memory on a GPU when its address is first resolved there -- inside
+// lcg_static_reserve() or the first lcg_gemm_r7_static call on that device -- and keeps
+// it until the process exits.  A host that sizes its own pool from the free memory
+// calls lcg_static_reserve() on every device first (or runs with
+// CUDA_MODULE_LOADING=EAGER, which takes the memory when the library is loaded).
 #include <mutex>
 
 #include "lcg_common.h"
@@ -50,6 +54,11 @@ int scratch_address(void** out) {
 using namespace lcg;
 
 extern "C" int64_t lcg_static_scratch_bytes(void) { return LCG_STATIC_SCRATCH_BYTES; }
+
+extern "C" int lcg_static_reserve(void) {
+  void* planes = nullptr;
+  return scratch_address(&planes);
+}
 
 extern "C" int lcg_gemm_r7_static(const lcg_scheme_t* scheme, const void* a, int64_t lda,
                                   const void* b_planes, int64_t ld_b, void* c, int64_t ldc,

@@ -58,6 +58,7 @@ SIGNATURES = {
     "lcg_gemm_r7_static": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _i32,
                                   _vp, _vp]),
     "lcg_static_scratch_bytes": (_i64, []),
+    "lcg_static_reserve": (_i32, []),
     "lcg_add_rmsnorm": (_i32, [_vp, _vp, _vp, _i64, _i64, _f32, _vp, _vp, _vp]),
     "lcg_swiglu": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "lcg_add": (_i32, [_vp, _vp, _vp, _i64, _vp]),

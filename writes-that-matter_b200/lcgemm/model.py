@@ -15,6 +15,9 @@ Arms of :meth:`RandomInitDecoder.prefill`:
 ``"eager"``   the same layer as plain torch ops, the functional reference itself;
 ``"rank7"``   the chained rank-7 plans of this package (one ``build_chain`` for the model, B
               planes prepared per layer at :meth:`install`, as ``qwen_patch._prepare`` does);
+``"rank7_allranks"``  the same plans on the all-ranks schedule for both GEMMs: every C block
+              has one writer and a fixed order of additions, so the result is reproducible bit
+              for bit (slower: ``down`` then has fewer tiles than the GPU has CTA pairs);
 ``"dense"``   the stock layer on this package's dense tcgen05 GEMM.
 
 The input norm of every layer uses the fused add + RMSNorm kernel in all arms.
@@ -27,6 +30,7 @@ import torch
 import torch.nn.functional as F
 
 from . import ops
+from ._native import SCHEDULE_ALL_RANKS
 from .seams import build_chain
 
 
@@ -81,6 +85,7 @@ class RandomInitDecoder:
                 o=w(cfg.hidden, cfg.q_heads * cfg.head_dim), post_norm=w(cfg.hidden, scale=0.01),
                 gate_up=w(2 * cfg.inter, cfg.hidden), down=w(cfg.hidden, cfg.inter)))
         self._plans = {}
+        self._plans_det = {}
         self._dense = {}
         self.calls = {"fused": 0, "reference": 0}
 
@@ -89,6 +94,11 @@ class RandomInitDecoder:
         """Plans for one exact prefill length and B planes for every layer."""
         cfg = self.cfg
         gate, down = build_chain((tokens, cfg.hidden, 2 * cfg.inter), (tokens, cfg.inter, cfg.hidden))
+        det_gate, det_down = build_chain((tokens, cfg.hidden, 2 * cfg.inter), (tokens, cfg.inter, cfg.hidden))
+        det_gate.schedule = SCHEDULE_ALL_RANKS
+        det_down.rank_split = False
+        det_gate.preclear = det_gate.c                    # an all-ranks consumer initialises its own output
+        self._plans_det[tokens] = (det_gate, det_down)
         nbytes = 0
         for layer in self.layers:
             if "gate_bw" not in layer:
@@ -104,8 +114,8 @@ class RandomInitDecoder:
     def _mlp(self, arm: str, layer: dict, delta, residual, ring):
         cfg = self.cfg
         m = delta.shape[0]
-        if arm == "rank7" and m in self._plans:
-            gate, down = self._plans[m]
+        if arm in ("rank7", "rank7_allranks") and m in self._plans:
+            gate, down = self._plans[m] if arm == "rank7" else self._plans_det[m]
             self.calls["fused"] += 1
             res_out = ring[0]
             ring.reverse()
@@ -131,11 +141,11 @@ class RandomInitDecoder:
     @torch.no_grad()
     def prefill(self, token_ids: torch.Tensor, arm: str = "stock"):
         """Batch-1 prefill; returns (logits of the last position as fp32, final hidden state)."""
-        if arm not in ("stock", "eager", "rank7", "dense"):
+        if arm not in ("stock", "eager", "rank7", "rank7_allranks", "dense"):
             raise ValueError(f"unknown arm {arm!r}")
         cfg = self.cfg
         m = token_ids.shape[0]
-        if arm == "rank7" and m not in self._plans:
+        if arm in ("rank7", "rank7_allranks") and m not in self._plans:
             raise RuntimeError(f"install({m}) before a rank-7 prefill of {m} tokens")
         pos = torch.arange(m, device=self.device, dtype=torch.float32)
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=self.device,

@@ -88,6 +88,11 @@ class HostStreamedLayer:
             cur.wait_event(ev)
 
     def drain(self) -> None:
+        """Wait for everything queued and raise if a device-side wait ran out on the way (under
+        tensor parallelism: a barrier between the ranks that a peer never reached)."""
+        from . import ops
+
         self.s_in.synchronize()
         self.s_out.synchronize()
         torch.cuda.current_stream().synchronize()
+        ops.check_status()

@@ -82,6 +82,7 @@ class PeerExchange:
 
         group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.tokens, self.hidden = tokens, hidden
         if self.world > 8:
             raise ValueError("the peer exchange supports at most 8 ranks")
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -120,7 +121,7 @@ class TensorParallelMlp:
 
     def __init__(self, tokens: int, norm_weight, gate_up_shard, down_shard, eps: float = 1e-6,
                  group=None, make_layer=None, add=None, slabs: int = 1, reserve_groups: int = 8,
-                 fused: bool = False):
+                 fused: bool = False, exchange: "PeerExchange | None" = None):
         if make_layer is None:
             from .layer import Rank7MlpLayer as make_layer
         self.group = group
@@ -138,7 +139,13 @@ class TensorParallelMlp:
             m, _, n = down.shape
             if n % 8 or not down.c.is_contiguous():
                 raise ValueError("the fused exchange needs a hidden size that is a multiple of 8")
-            self.exchange = PeerExchange(m, n, group)
+            # The symmetric buffers (3 * tokens * hidden * 2 bytes) may be shared by all the layers of
+            # a model that run one after the other on ONE stream: the second barrier of a layer call
+            # orders every rank's reads of the receive regions before the next call's pushes.
+            if exchange is not None and (exchange.tokens, exchange.hidden) != (m, n):
+                raise ValueError(f"the shared exchange is for {(exchange.tokens, exchange.hidden)}, "
+                                 f"this layer needs {(m, n)}")
+            self.exchange = exchange if exchange is not None else PeerExchange(m, n, group)
             gate = self.layer.gate_plan
             gate.preclear = gate.c                   # nothing to clear: the push GEMM initialises its output
 
@@ -166,6 +173,10 @@ class TensorParallelMlp:
         return self.out
 
     def _forward_fused(self, x, delta):
+        """Nothing here synchronises, so a barrier wait that ran out (status code 106: a rank that
+        never arrived) does not raise from this call; the owners then reduce receive regions
+        that are not complete.  Callers check ``ops.check_status()`` at a step boundary before
+        they use the output (``HostStreamedLayer.drain`` and ``bench.py`` do)."""
         from . import ops
 
         lay, ex = self.layer, self.exchange
