@@ -748,23 +748,25 @@ def sustained_block(arms, seconds, device_index, block_s=0.4):
 def gemm_only_block(tokens, hidden, inter, steps, warmup, flush, device):
     """The two GEMMs of the layer without their seams: the rank-7 GEMM from operands that are
     already in place (gate_up: A planes written beforehand; down: planes written beforehand, and
-    the form that builds its A operands inside the kernel from the activation matrix) against
+    the form whose plane warps build the A planes inside the kernel from the activation matrix) against
     the dense tcgen05 GEMM on the same inputs.  Cold L2, arms interleaved."""
     from lcgemm import ops, scheme as S
 
     bf = torch.bfloat16
     x, _, wgu, wd = make_layer_tensors(tokens, hidden, inter, device)
     cse, loc = S.load("2x2_postsum_cse"), S.load("2x2_locality_ordered")
+    lead = S.load("2x2_locality_lead_single")
     s_act = torch.randn((tokens, inter), device=device).to(bf)
     a_pl, d_pl = ops.a_planes(x, cse), ops.a_planes(s_act, loc)
-    bp_g, bp_d = ops.prepare_b(wgu, cse), ops.prepare_b(wd, loc)
+    bp_g, bp_d, bp_l = ops.prepare_b(wgu, cse), ops.prepare_b(wd, loc), ops.prepare_b(wd, lead)
+    scr = torch.empty(ops.ahead_scratch_bytes(lead, tokens, inter), dtype=torch.uint8, device=device)
     z = torch.empty((tokens, 2 * inter), device=device, dtype=bf)
     o = torch.empty((tokens, hidden), device=device, dtype=bf)
     arms = {
         "gate_up_rank7": lambda: ops.gemm_r7_planes(cse, a_pl, bp_g, tokens, 2 * inter, hidden, out=z),
         "gate_up_dense_tcgen05": lambda: ops.gemm_dense(x, wgu, out=z),
         "down_rank7_planes": lambda: ops.gemm_r7_planes(loc, d_pl, bp_d, tokens, hidden, inter, out=o),
-        "down_rank7_fused_a": lambda: ops.gemm_r7_fused(s_act, bp_d, hidden, loc, out=o),
+        "down_rank7_ahead": lambda: ops.gemm_r7_ahead(s_act, bp_l, hidden, lead, out=o, scratch=scr),
         "down_dense_tcgen05": lambda: ops.gemm_dense(s_act, wd, out=o),
     }
     for fn in arms.values():
@@ -780,7 +782,7 @@ def gemm_only_block(tokens, hidden, inter, steps, warmup, flush, device):
     return {"tokens": tokens, "ms": t, "note": "operands in place, no seams; hybrid schedule",
             "gate_up_speedup_pct": (t["gate_up_dense_tcgen05"] / t["gate_up_rank7"] - 1) * 100,
             "down_planes_speedup_pct": (t["down_dense_tcgen05"] / t["down_rank7_planes"] - 1) * 100,
-            "down_fused_a_speedup_pct": (t["down_dense_tcgen05"] / t["down_rank7_fused_a"] - 1) * 100}
+            "down_ahead_speedup_pct": (t["down_dense_tcgen05"] / t["down_rank7_ahead"] - 1) * 100}
 
 
 def tp1_same_config(steps, warmup, flush, device):
@@ -894,18 +896,20 @@ def run_case(args, device):
 
 
 def run_sweep(args, device):
-    """The bare-GEMM sweep: the rank-7 GEMM in both of its forms -- A planes written by a pass in
-    front of the GEMM (postsum-CSE scheme), and A operands formed inside the GEMM kernel
-    (locality-ordered scheme, where the shape allows it) -- against the dense tcgen05 GEMM and
-    cuBLAS, odd shapes included; B planes prepared offline.  One JSON line per shape; `rank7_ms`
-    is the form `lcgemm.ops.bare_gemm_form` dispatches that shape to."""
-    from lcgemm import ops, scheme as S
+    """The bare-GEMM sweep: the rank-7 GEMM in its forms -- A planes written by a pass in front
+    of the GEMM (postsum-CSE scheme); A planes formed by the GEMM kernel's own plane warps one
+    product ahead of the MMAs (locality-ordered products, single-block ones first; both unit
+    lists); with --sweep-fused also the form that builds the A operand tiles in shared memory --
+    against the dense tcgen05 GEMM and cuBLAS, odd shapes included; B planes prepared offline.
+    One JSON line per shape; `rank7_ms` is the form `lcgemm.ops.bare_gemm_form` dispatches that
+    shape to."""
+    from lcgemm import _native as nat, ops, scheme as S
 
     flush = torch.empty(FLUSH_BYTES, dtype=torch.int8, device=device)
     kn_list = [kn for kn in SWEEP_KN if args.sweep_kn is None or f"{kn[0]}x{kn[1]}" in args.sweep_kn.split(",")]
     for m in (2048, 4096, 8192):
         for k, n in kn_list:
-            sch, sch_f = S.load("2x2_postsum_cse"), S.load("2x2_locality_ordered")
+            sch, sch_a = S.load("2x2_postsum_cse"), S.load("2x2_locality_lead_single")
             g = torch.Generator(device=device).manual_seed(m + k + n)
             a = torch.randn((m, k), generator=g, device=device).to(torch.bfloat16)
             w = (torch.randn((n, k), generator=g, device=device) * 0.02).to(torch.bfloat16)
@@ -915,14 +919,19 @@ def run_sweep(args, device):
             out = torch.empty((m, ld), device=device, dtype=torch.bfloat16)[:, :n]
             cb_out = torch.empty((m, n), device=device, dtype=torch.bfloat16)
             arms = {
-                "rank7_planes": lambda: ops.gemm_r7(a, bp, n, sch, out=out, a_workspace=ws, fused=False),
+                "rank7_planes": lambda: ops.gemm_r7(a, bp, n, sch, out=out, a_workspace=ws, form="planes"),
                 "dense_tcgen05": lambda: ops.gemm_dense(a, w, out=out),
                 "dense_cublas": lambda: torch.matmul(a, w.t(), out=cb_out),
             }
-            fused_ok = ops.fused_a_supported(sch_f, m, n, k)
-            if fused_ok:
-                bp_f = ops.prepare_b(w, sch_f)
-                arms["rank7_fused"] = lambda: ops.gemm_r7_fused(a, bp_f, n, sch_f, out=out)
+            need = ops.ahead_scratch_bytes(sch_a, m, k)
+            if need > 0:
+                bp_a = ops.prepare_b(w, sch_a)
+                scr = torch.empty(need, dtype=torch.uint8, device=device)
+                arms["rank7_ahead_hybrid"] = lambda: ops.gemm_r7_ahead(a, bp_a, n, sch_a, out=out, scratch=scr)
+                arms["rank7_ahead_split"] = lambda: ops.gemm_r7_ahead(a, bp_a, n, sch_a, out=out, scratch=scr,
+                                                                      schedule=nat.SCHEDULE_RANK_SPLIT)
+                if args.sweep_fused:
+                    arms["rank7_fused"] = lambda: ops.gemm_r7_fused(a, bp_a, n, sch_a, out=out)
             for fn in arms.values():
                 for _ in range(args.warmup):
                     fn()
@@ -933,25 +942,28 @@ def run_sweep(args, device):
                     times[name] += _event_times(fn, 1, 0, flush)
             ops.check_status()
             t = {name: statistics.mean(v) for name, v in times.items()}
-            form = ops.bare_gemm_form(m, n, k)
-            r7 = t["rank7_fused"] if form[1] and fused_ok else t["rank7_planes"]
+            name, form, schedule = ops.bare_gemm_form(m, n, k)
+            if form == "ahead" and need > 0:
+                r7 = t["rank7_ahead_split" if schedule == nat.SCHEDULE_RANK_SPLIT else "rank7_ahead_hybrid"]
+            else:
+                form, r7 = "planes", t["rank7_planes"]
             dn, cb = t["dense_tcgen05"], t["dense_cublas"]
             fl = 2.0 * m * n * k
+            pct = lambda key: (dn / t[key] - 1) * 100 if key in t else None
             print(json.dumps({
-                "sweep": "bare_gemm", "M": m, "K": k, "N": n, "schedule": "hybrid",
-                "dispatch": {"scheme": form[0], "fused_a": bool(form[1] and fused_ok)},
-                "rank7_ms": r7, "rank7_planes_ms": t["rank7_planes"], "rank7_fused_ms": t.get("rank7_fused"),
-                "dense_tcgen05_ms": dn, "dense_cublas_ms": cb,
+                "sweep": "bare_gemm", "M": m, "K": k, "N": n,
+                "dispatch": {"scheme": name, "form": form,
+                             "schedule": {0: "all_ranks", 1: "rank_split", 2: "hybrid"}[schedule]},
+                "rank7_ms": r7, "ms": t,
                 "rank7_effective_tflops": fl / r7 / 1e9, "rank7_executed_tflops": 0.875 * fl / r7 / 1e9,
                 "dense_tcgen05_tflops": fl / dn / 1e9, "dense_cublas_tflops": fl / cb / 1e9,
                 "speedup_vs_dense_tcgen05_pct": (dn / r7 - 1) * 100, "speedup_vs_cublas_pct": (cb / r7 - 1) * 100,
-                "fused_vs_dense_tcgen05_pct": (dn / t["rank7_fused"] - 1) * 100 if fused_ok else None,
-                "planes_vs_dense_tcgen05_pct": (dn / t["rank7_planes"] - 1) * 100,
-                "note": "rank7_planes time includes forming the A planes; L2 flushed between timed launches"}),
+                "vs_dense_tcgen05_pct": {key: pct(key) for key in t if key.startswith("rank7_")},
+                "note": "rank7_planes includes the plane-forming pass; L2 flushed between timed launches"}),
                 flush=True)
             del a, w, bp, ws, out, cb_out, arms
-            if fused_ok:
-                del bp_f
+            if need > 0:
+                del bp_a, scr
             torch.cuda.empty_cache()
 
 
@@ -1177,6 +1189,8 @@ def main():
                     help="time one kernel alone: gate_up | down | norm_planes | a_planes | dense_gate_up")
     ap.add_argument("--tokens", type=int, default=4096, help="token count for --case")
     ap.add_argument("--sweep", action="store_true", help="bare-GEMM shape sweep, odd shapes included")
+    ap.add_argument("--sweep-fused", action="store_true",
+                    help="--sweep: also time the form that builds the A operand tiles in shared memory (slow)")
     ap.add_argument("--sweep-kn", default=None,
                     help="restrict --sweep to these KxN pairs, comma separated (e.g. 17408x5120,16384x6144)")
     ap.add_argument("--gpus", type=int, default=1)

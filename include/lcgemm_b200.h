@@ -176,6 +176,26 @@ int lcg_gemm_r7_fused(const lcg_scheme_t* scheme, const void* a, int64_t lda,
 /* 1 when lcg_gemm_r7_fused accepts this scheme and shape, else 0. */
 int lcg_gemm_r7_fused_supported(const lcg_scheme_t* scheme, int64_t M, int64_t N, int64_t K);
 
+/* Rank-7 C = A @ B^T from the activation matrix with the plane-forming pass folded into the
+ * GEMM kernel: while the MMAs work on one product, eight otherwise idle warps of every CTA form
+ * the A plane of the next two-term product (16-byte loads of its two blocks, one packed bf16 add
+ * or subtract, 16-byte stores) into `scratch`, from where the TMA producer loads it, L2-hot, once
+ * a chunk counter says the plane is whole; products whose A row is a single block with
+ * coefficient +1 are loaded from `a` itself.  Same arithmetic and rounding as lcg_a_planes +
+ * lcg_gemm_r7 (bit-equal with LCG_SCHEDULE_ALL_RANKS), without the separate pass in front of the
+ * GEMM that those two pay for (lcgemm/planes.py:27-50, lcgemm/kernels/sm100.py:578-592).
+ * A scheme whose first products are single-block ones (2x2_locality_lead_single) starts without
+ * waiting.  scratch: lcg_gemm_r7_ahead_scratch_bytes() bytes, 256-byte aligned, owned by the
+ * caller; the first 256 bytes are cleared on the stream by this call.  Needs K % 128 == 0, A-side
+ * rows of one or two +-1 terms, a 16-byte aligned with lda % 8 == 0.  All waits are bounded
+ * (status code 107: a plane never became whole). */
+int lcg_gemm_r7_ahead(const lcg_scheme_t* scheme, const void* a, int64_t lda,
+                      const void* b_planes, int64_t ld_b, void* c, int64_t ldc,
+                      int64_t M, int64_t N, int64_t K, void* scratch, int64_t scratch_bytes,
+                      int schedule, int cta_group, int32_t* status, void* stream);
+/* Bytes of scratch lcg_gemm_r7_ahead needs, or -1 when it does not take this scheme / shape. */
+int64_t lcg_gemm_r7_ahead_scratch_bytes(const lcg_scheme_t* scheme, int64_t M, int64_t K);
+
 /* lcg_gemm_r7 restricted to the tile rows [tile_row_begin, tile_row_end) of both block rows
  * (a tile row is 128 * cta_group rows of a block row: output rows i * M2 + [begin, end) * 256
  * for i = 0, 1 with the default pairing; tile_row_end < 0 means "to the last"), on at most

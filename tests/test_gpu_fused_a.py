@@ -113,3 +113,74 @@ def test_fused_full_size_properties(lc):
     assert bool((cz[100:164] == 0).all()) and bool((cz[m // 2 + 100:m // 2 + 164] == 0).all())
     ones = torch.ones(n, device="cuda")
     assert rel_fro(c.float() @ ones, a.float() @ (w.float().T @ ones)) < 2e-2
+
+
+# ------------------------------------------------------------- product-ahead form
+AHEAD_NAMES = ("2x2_locality_ordered", "2x2_locality_lead_single")
+
+
+@pytest.mark.parametrize("name", AHEAD_NAMES)
+@pytest.mark.parametrize("group", [1, 2])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_ahead_equals_plane_path_bit_for_bit(lc, name, group, shape):
+    """``lcg_gemm_r7_ahead``: the plane warps of all CTAs form each two-term A plane in a global
+    scratch one product ahead of the MMAs.  Same values as ``lcg_a_planes`` writes, so the
+    deterministic schedule must give the plane path's bits."""
+    m, n, k = shape
+    sch = lc.load(name)
+    a, w = seeded((m, k), 31), seeded((n, k), 32, 0.02)
+    bp = lc.planes.prepare_b(w, sch)
+    need = lc.ops.ahead_scratch_bytes(sch, m, k)
+    assert need == 256 + 5 * ((m + 1) // 2) * (k // 2) * 2
+    scratch = torch.full((need,), 0xA5, dtype=torch.uint8, device="cuda")      # stale contents
+    got = lc.ops.gemm_r7_ahead(a, bp, n, sch, scratch=scratch, schedule=0, cta_group=group)
+    want = lc.ops.gemm_r7(a, bp, n, sch, schedule=0, cta_group=group, fused=False)
+    assert torch.equal(got, want)
+    again = lc.ops.gemm_r7_ahead(a, bp, n, sch, scratch=scratch, schedule=0, cta_group=group)
+    assert torch.equal(again, want)                       # counters are cleared by every call
+
+
+@pytest.mark.parametrize("name", AHEAD_NAMES)
+@pytest.mark.parametrize("schedule", [0, 1, 2])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_ahead_against_oracle(lc, name, schedule, shape):
+    m, n, k = shape
+    sch, tb = lc.load(name), O.Tables(name)
+    a, w = seeded((m, k), 33), seeded((n, k), 34, 0.02)
+    bp = lc.planes.prepare_b(w, sch)
+    c = lc.ops.gemm_r7_ahead(a, bp, n, sch, schedule=schedule)
+    assert rel_fro(c, a.double().cpu() @ w.double().cpu().T) <= TOL_R7_DENSE
+    model = O.scheme_matmul(a.cpu(), w.cpu(), tb, mode="kernel_split" if schedule == 1 else "kernel")
+    assert rel_fro(c, model) <= (TOL_R7_ORACLE_SPLIT if schedule else TOL_R7_ORACLE)
+
+
+def test_ahead_refuses_small_scratch_and_other_schemes(lc):
+    m, n, k = 256, 512, 256
+    sch = lc.load(NAME)
+    a, w = seeded((m, k), 35), seeded((n, k), 36, 0.02)
+    bp = lc.planes.prepare_b(w, sch)
+    with pytest.raises(ValueError):
+        lc.ops.gemm_r7_ahead(a, bp, n, sch, scratch=torch.empty(1024, dtype=torch.uint8, device="cuda"))
+    cse = lc.load("2x2_postsum_cse")
+    assert lc.ops.ahead_scratch_bytes(cse, m, k) == -1
+    with pytest.raises(ValueError):
+        lc.ops.gemm_r7_ahead(a, lc.planes.prepare_b(w, cse), n, cse)
+
+
+def test_ahead_full_size_properties(lc):
+    m, n, k = 4096, 5120, 17408
+    sch = lc.load("2x2_locality_lead_single")
+    a = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+    w = (torch.randn((n, k), device="cuda") * 0.02).to(torch.bfloat16)
+    bp = lc.planes.prepare_b(w, sch)
+    scratch = torch.empty(lc.ops.ahead_scratch_bytes(sch, m, k), dtype=torch.uint8, device="cuda")
+    c = lc.ops.gemm_r7_ahead(a, bp, n, sch, scratch=scratch, schedule=0).clone()
+    assert torch.equal(c, lc.ops.gemm_r7(a, bp, n, sch, schedule=0, fused=False))
+    d = lc.ops.gemm_dense(a, w)
+    assert rel_fro(c[:, ::7], d[:, ::7]) <= TOL_R7_DENSE
+    c2 = lc.ops.gemm_r7_ahead((a.float() * 2).to(torch.bfloat16), bp, n, sch, scratch=scratch, schedule=0)
+    assert torch.equal(c2.float(), c.float() * 2)
+    ch = lc.ops.gemm_r7_ahead(a, bp, n, sch, scratch=scratch, schedule=2)
+    assert rel_fro(ch, c) < 4e-3
+    ones = torch.ones(n, device="cuda")
+    assert rel_fro(c.float() @ ones, a.float() @ (w.float().T @ ones)) < 2e-2

@@ -75,7 +75,7 @@ struct Roles {
 
 // Codes left in the status word by a wait that ran out.
 constexpr int kCodeProducer = 101, kCodeMmaAcc = 102, kCodeMmaFull = 103, kCodeEpilogue = 104,
-              kCodePlane = 105;
+              kCodePlane = 105, kCodeAhead = 107;
 
 template <int kCtaGroup>
 struct Tile {
@@ -134,7 +134,16 @@ struct FuseParams {
   int8_t simt[kMaxRank];
   int8_t blk[kMaxRank][2];
   int8_t neg[kMaxRank][2];
-  int32_t debug;
+  // Product-ahead form: the two-term products' planes are written to `scratch` (plane slot[r] at
+  // rows slot[r] * m2, leading dimension k2) by the plane warps of all CTAs, one product ahead of
+  // the MMAs; counters[r] counts the finished chunks of product r's plane (`chunks` when complete).
+  __nv_bfloat16* scratch;
+  uint32_t* counters;
+  int32_t chunks;
+  int32_t chunk_rows;
+  int8_t slot[kMaxRank];      // -1: single +1 term, read from `a` itself
+  int8_t order[kMaxRank];     // products with a plane slot, in the order the steps first need them
+  int32_t nslots;
 };
 
 struct GemmParams {
@@ -370,11 +379,15 @@ __device__ __forceinline__ void push_rows32(const PushParams& pp, int tn, int ro
 
 // kMode: 0 plain GEMM; 1 chained (plane warps form SwiGLU + the consumer's planes behind each
 // tile); 2 push (the same warps copy each finished tile to the rank that owns its rows);
-// 3 fused A (the same warps form the A operand tiles from the activation matrix's blocks).
-constexpr int kModePlain = 0, kModePlanes = 1, kModePush = 2, kModeFusedA = 3;
+// 3 fused A (the same warps form the A operand tiles from the activation matrix's blocks);
+// 4 product-ahead A (the same warps of all CTAs form the A plane of the product after the one the
+// MMAs are on into a global scratch, which the TMA producer reads once its chunk counter is full).
+constexpr int kModePlain = 0, kModePlanes = 1, kModePush = 2, kModeFusedA = 3, kModeAheadA = 4;
 // K blocks whose loads a fused-A producer thread keeps in flight in registers ahead of the block
 // it is writing into shared memory.
 constexpr int kFuseDepth = 2;
+// Vectors of each block a plane-ahead thread keeps in flight.
+constexpr int kAheadUnroll = 8;
 
 __device__ __forceinline__ uint32_t bf16x2_add(uint32_t a, uint32_t b) {
   uint32_t r;
@@ -389,7 +402,8 @@ __device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
 template <int kCtaGroup, int kMode, unsigned long long kPlaneCode = 0>
 __global__ void __launch_bounds__(kMode != kModePlain ? kThreadsChain : kThreadsPlain, 1)
 k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-       const __grid_constant__ CMaps tma_c, const __grid_constant__ GemmParams p) {
+       const __grid_constant__ CMaps tma_c, const __grid_constant__ GemmParams p,
+       const __grid_constant__ CUtensorMap tma_a2) {
   using T = Tile<kCtaGroup>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -438,6 +452,7 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
     misc_gen[3] = 0u;
     fence_mbar_init();
     prefetch_tensormap(&tma_a);
+    if constexpr (kMode == kModeAheadA) prefetch_tensormap(&tma_a2);
     prefetch_tensormap(&tma_b);
     prefetch_tensormap(&tma_c.m[0]);
   }
@@ -483,18 +498,34 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
             a_row = (blk >> 1) * p.fuse.m2 + uc.tm * T::kTileM + static_cast<int>(cta_rank) * kBM;
             a_col_off = (blk & 1) * p.fuse.k2;
           }
+          const CUtensorMap* a_map = &tma_a;
+          if constexpr (kMode == kModeAheadA) {
+            const int slot = p.fuse.slot[sd.a_plane];
+            const int tile_row = uc.tm * T::kTileM + static_cast<int>(cta_rank) * kBM;
+            if (slot < 0) {             // single block, coefficient +1: straight from the matrix
+              const int blk = p.fuse.blk[sd.a_plane][0];
+              a_row = (blk >> 1) * p.fuse.m2 + tile_row;
+              a_col_off = (blk & 1) * p.fuse.k2;
+            } else {                    // the plane the plane warps have been forming: wait until it is whole
+              a_map = &tma_a2;
+              a_row = slot * p.fuse.m2 + tile_row;
+              global_counter_wait(p.fuse.counters + sd.a_plane, static_cast<uint32_t>(p.fuse.chunks), ctl,
+                                  kCodeAhead);
+              fence_proxy_async_all();  // the planes were written through the generic proxy; TMA reads them
+            }
+          }
           const uint32_t bytes = load_a ? T::kStageBytes : T::kBBytes;
           for (int kb = uc.kb0; kb < uc.kb1; ++kb, kcol += kBK) {
             mbar_wait(empty_bar(stage), wait_parity, ctl, kCodeProducer);
             const uint32_t sa = a_smem(stage);
             if constexpr (kCtaGroup == 1) {
               mbar_arrive_expect_tx(full_bar(stage), bytes);
-              if (load_a) tma_load_2d(sa, &tma_a, full_bar(stage), kcol + a_col_off, a_row);
+              if (load_a) tma_load_2d(sa, a_map, full_bar(stage), kcol + a_col_off, a_row);
               tma_load_2d(sa + T::kABytes, &tma_b, full_bar(stage), kcol, b_row);
             } else {
               if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * bytes);
               const uint32_t bar = full_remote0 + 8u * stage;
-              if (load_a) tma_load_2d_pair(sa, &tma_a, bar, kcol + a_col_off, a_row);
+              if (load_a) tma_load_2d_pair(sa, a_map, bar, kcol + a_col_off, a_row);
               tma_load_2d_pair(sa + T::kABytes, &tma_b, bar, kcol, b_row);
             }
             if (++stage == T::kStages) {
@@ -721,8 +752,8 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
       auto w_issue = [&](uint4 (&dst)[2][4]) -> uint32_t {
         if (!w_valid) return kNone;
         const uint32_t meta = w_meta;
-        if ((meta & 1u) && fp.debug != 1) {
-          const int nterm = fp.debug == 3 ? 1 : static_cast<int>((meta >> 1) & 3u);
+        if (meta & 1u) {
+          const int nterm = static_cast<int>((meta >> 1) & 3u);
 #pragma unroll
           for (int t = 0; t < 2; ++t)
 #pragma unroll
@@ -789,6 +820,71 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
             wait_parity ^= 1u;
           }
           meta[d] = w_issue(buf[d]);
+        }
+      }
+    }
+  } else if constexpr (kMode == kModeAheadA) {
+    if (plane_warp >= 0) {
+      // ----------------------------------------------- plane warps, one product ahead
+      // The two-term products' A planes, in the order the steps need them.  A plane is cut
+      // into chunks of `chunk_rows` rows; chunk c belongs to CTA c mod gridDim.x.  These warps
+      // never wait for anything, so every counter fills whatever the MMA side is doing.
+      const FuseParams& fp = p.fuse;
+      const int ptid = plane_warp * 32 + lane;
+      const int nvec = fp.k2 >> 3;
+      for (int o = 0; o < fp.nslots; ++o) {
+        const int r = fp.order[o];
+        const int b0 = fp.blk[r][0], b1 = fp.blk[r][1];
+        const bool neg0 = fp.neg[r][0] != 0, neg1 = fp.neg[r][1] != 0;
+        const __nv_bfloat16* src0 = fp.a + static_cast<int64_t>(b0 >> 1) * fp.m2 * fp.lda +
+                                    static_cast<int64_t>(b0 & 1) * fp.k2;
+        const __nv_bfloat16* src1 = fp.a + static_cast<int64_t>(b1 >> 1) * fp.m2 * fp.lda +
+                                    static_cast<int64_t>(b1 & 1) * fp.k2;
+        const int rows0 = (b0 >> 1) ? fp.m - fp.m2 : fp.m2;     // rows block row b >> 1 really has
+        const int rows1 = (b1 >> 1) ? fp.m - fp.m2 : fp.m2;
+        __nv_bfloat16* dst = fp.scratch + static_cast<int64_t>(fp.slot[r]) * fp.m2 * fp.k2;
+        for (int c = static_cast<int>(blockIdx.x); c < fp.chunks; c += static_cast<int>(gridDim.x)) {
+          // The chunk's rows x vectors as one index space, kAheadUnroll vectors of each block in
+          // flight per thread (the loads' round trip, not their issue rate, sets the pace).
+          const int row0 = c * fp.chunk_rows;
+          const int total = (min(row0 + fp.chunk_rows, fp.m2) - row0) * nvec;
+          for (int base = ptid; base < total; base += kPlaneThreads * kAheadUnroll) {
+            uint4 x[kAheadUnroll], y[kAheadUnroll];
+            int64_t doff[kAheadUnroll];
+#pragma unroll
+            for (int u = 0; u < kAheadUnroll; ++u) {
+              const int e = base + u * kPlaneThreads;
+              const int row = row0 + e / nvec;
+              const int v = e - (e / nvec) * nvec;
+              const bool in = e < total;
+              doff[u] = in ? static_cast<int64_t>(row) * fp.k2 + v * 8 : -1;
+              x[u] = (in && row < rows0)
+                         ? __ldcs(reinterpret_cast<const uint4*>(src0 + static_cast<int64_t>(row) * fp.lda) + v)
+                         : make_uint4(0u, 0u, 0u, 0u);
+              y[u] = (in && row < rows1)
+                         ? __ldcs(reinterpret_cast<const uint4*>(src1 + static_cast<int64_t>(row) * fp.lda) + v)
+                         : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < kAheadUnroll; ++u) {
+              uint4 q = x[u];
+              if (neg0) q.x ^= 0x80008000u, q.y ^= 0x80008000u, q.z ^= 0x80008000u, q.w ^= 0x80008000u;
+              if (neg1) {
+                q.x = bf16x2_sub(q.x, y[u].x), q.y = bf16x2_sub(q.y, y[u].y);
+                q.z = bf16x2_sub(q.z, y[u].z), q.w = bf16x2_sub(q.w, y[u].w);
+              } else {
+                q.x = bf16x2_add(q.x, y[u].x), q.y = bf16x2_add(q.y, y[u].y);
+                q.z = bf16x2_add(q.z, y[u].z), q.w = bf16x2_add(q.w, y[u].w);
+              }
+              if (doff[u] >= 0) *reinterpret_cast<uint4*>(dst + doff[u]) = q;
+            }
+          }
+          // Publish the chunk: every writer orders its stores before the async proxy's later
+          // reads and makes them visible GPU-wide, then one thread counts the chunk.
+          fence_proxy_async_all();
+          __threadfence();
+          named_bar_sync(2, kPlaneThreads);
+          if (ptid == 0) atomicAdd(fp.counters + r, 1u);
         }
       }
     }
@@ -977,7 +1073,7 @@ int pick_group_m(int tiles_m, int groups) {
 
 template <int kCtaGroup, int kMode, unsigned long long kPlaneCode = 0>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CMaps& mc, GemmParams& p,
-           cudaStream_t stream) {
+           cudaStream_t stream, const CUtensorMap* ma2 = nullptr) {
   using T = Tile<kCtaGroup>;
   constexpr bool kChain = kMode != kModePlain;
   auto kern = k_gemm<kCtaGroup, kMode, kPlaneCode>;
@@ -1004,7 +1100,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CMaps& mc, GemmPa
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  LCG_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, p));
+  LCG_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, p, ma2 != nullptr ? *ma2 : ma));
   count_launch();
   return LCG_OK;
 }
@@ -1238,7 +1334,6 @@ static int fill_fuse(const lcg_scheme* scheme, const void* a, int64_t lda, int64
     f->nterm[r] = static_cast<int8_t>(n);
     f->simt[r] = !(n == 1 && !f->neg[r][0]);
   }
-  if (const char* dbg = getenv("LCG_FUSE_DEBUG")) f->debug = atoi(dbg);
   return LCG_OK;
 }
 
@@ -1285,6 +1380,87 @@ extern "C" int lcg_gemm_r7_fused(const lcg_scheme_t* scheme, const void* a, int6
   auto st_ = static_cast<cudaStream_t>(stream);
   if (int e = zero_tail_tiles(p, c, ldc, M, N, g, cta_group, st_)) return e;
   return cta_group == 1 ? launch<1, kModeFusedA>(ma, mb, mc, p, st_) : launch<2, kModeFusedA>(ma, mb, mc, p, st_);
+}
+
+// ---- product-ahead form: scratch layout = [256 bytes: chunk counters][planes of the two-term products]
+constexpr int64_t kAheadHeaderBytes = 256;
+constexpr int kAheadChunkRows = 4;
+
+extern "C" int64_t lcg_gemm_r7_ahead_scratch_bytes(const lcg_scheme_t* scheme, int64_t M, int64_t K) {
+  if (!scheme || M < 2 || K < 128 || K % 128 != 0) return -1;
+  int slots = 0;
+  for (int r = 0; r < scheme->rank; ++r) {
+    int n = 0, neg = 0;
+    for (int x = 0; x < 4; ++x) {
+      n += scheme->a[r][x] != 0;
+      neg |= scheme->a[r][x] < 0;
+    }
+    if (n < 1 || n > 2) return -1;
+    if (!(n == 1 && !neg)) ++slots;
+  }
+  const int64_t m2 = (M + 1) / 2;
+  return kAheadHeaderBytes + slots * m2 * (K / 2) * 2;
+}
+
+extern "C" int lcg_gemm_r7_ahead(const lcg_scheme_t* scheme, const void* a, int64_t lda,
+                                 const void* b_planes, int64_t ld_b, void* c, int64_t ldc, int64_t M,
+                                 int64_t N, int64_t K, void* scratch, int64_t scratch_bytes,
+                                 int schedule, int cta_group, int32_t* status, void* stream) {
+  if (!scheme || !a || !b_planes || !c || !scratch) return fail(LCG_ERR_BAD_ARG, "NULL operand");
+  if (schedule != LCG_SCHEDULE_ALL_RANKS && schedule != LCG_SCHEDULE_RANK_SPLIT &&
+      schedule != LCG_SCHEDULE_HYBRID)
+    return fail(LCG_ERR_BAD_ARG, "unknown schedule %d", schedule);
+  cta_group = resolve_group(cta_group);
+  if (cta_group != 1 && cta_group != 2) return fail(LCG_ERR_BAD_ARG, "cta_group must be 0, 1 or 2");
+  if (K < 128 || K % 128 != 0)
+    return fail(LCG_ERR_UNSUPPORTED_SHAPE,
+                "the in-kernel A planes cover whole 64-column K blocks of each half of A: K %% 128 must "
+                "be 0, got K=%lld (use lcg_a_planes + lcg_gemm_r7)", (long long)K);
+  if ((reinterpret_cast<uintptr_t>(a) & 15u) != 0 || lda % 8 != 0)
+    return fail(LCG_ERR_MISALIGNED, "A must be 16-byte aligned with lda %% 8 == 0");
+  if ((reinterpret_cast<uintptr_t>(scratch) & 255u) != 0)
+    return fail(LCG_ERR_MISALIGNED, "scratch must be 256-byte aligned");
+  R7Geometry g;
+  if (int e = r7_geometry(M, N, K, &g)) return e;
+  if (ldc < N) return fail(LCG_ERR_BAD_ARG, "ldc below N");
+  if (lda < K || ld_b < g.k2p) return fail(LCG_ERR_BAD_ARG, "leading dimension below extent");
+  CUtensorMap ma, mb, ma2;
+  CMaps mc;
+  GemmParams p;
+  if (int e = fill_r7(scheme, a, lda, b_planes, ld_b, c, ldc, M, N, g, schedule, cta_group, &ma, &mb,
+                      &mc, &p, 0, -1, 0, K))
+    return e;
+  FuseParams& f = p.fuse;
+  if (int e = fill_fuse(scheme, a, lda, M, K, g, &f)) return e;
+  f.nslots = 0;
+  for (int r = 0; r < scheme->rank; ++r) {
+    f.slot[r] = -1;
+    if (f.simt[r]) {
+      f.slot[r] = static_cast<int8_t>(f.nslots);
+      f.order[f.nslots++] = static_cast<int8_t>(r);
+    }
+  }
+  const int64_t need = kAheadHeaderBytes + static_cast<int64_t>(f.nslots) * g.m2 * (K / 2) * 2;
+  if (scratch_bytes < need)
+    return fail(LCG_ERR_BAD_ARG, "scratch holds %lld bytes, this shape needs %lld "
+                "(lcg_gemm_r7_ahead_scratch_bytes)", (long long)scratch_bytes, (long long)need);
+  f.counters = static_cast<uint32_t*>(scratch);
+  f.scratch = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(scratch) + kAheadHeaderBytes);
+  f.chunk_rows = kAheadChunkRows;
+  f.chunks = static_cast<int32_t>((g.m2 + kAheadChunkRows - 1) / kAheadChunkRows);
+  p.status = status;
+  auto st_ = static_cast<cudaStream_t>(stream);
+  if (f.nslots > 0) {
+    if (int e = make_map(&ma2, f.scratch, K / 2, static_cast<int64_t>(f.nslots) * g.m2, K / 2, kBM,
+                         "A plane scratch"))
+      return e;
+  } else {
+    ma2 = ma;
+  }
+  LCG_CUDA_OK(cudaMemsetAsync(scratch, 0, kAheadHeaderBytes, st_));
+  if (int e = zero_tail_tiles(p, c, ldc, M, N, g, cta_group, st_)) return e;
+  return cta_group == 1 ? launch<1, kModeAheadA>(ma, mb, mc, p, st_, &ma2)
+                        : launch<2, kModeAheadA>(ma, mb, mc, p, st_, &ma2);
 }
 
 extern "C" int lcg_gemm_r7_slab(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,

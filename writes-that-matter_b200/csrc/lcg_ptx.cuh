@@ -154,6 +154,32 @@ __device__ __noinline__ void counter_wait(uint32_t addr, uint32_t at_least, cons
   }
 }
 
+// Bounded wait on a monotonically increasing counter in global memory that other CTAs of the
+// same (co-resident, persistent) grid advance with atomics after a __threadfence().
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __noinline__ void global_counter_wait(const uint32_t* ctr, uint32_t at_least,
+                                                 const WaitCtl& ctl, int code) {
+  if (ld_acquire_gpu(ctr) >= at_least) return;
+  if (*ctl.abort_flag) return;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (ld_acquire_gpu(ctr) < at_least) {
+    __nanosleep(200);
+    if ((++spins & 0x3fu) == 0) {
+      if (*ctl.abort_flag) return;
+      if (globaltimer_ns() - t0 > ctl.limit_ns) {
+        *ctl.abort_flag = 1u;
+        if (ctl.status != nullptr) atomicCAS(ctl.status, 0, code);
+        return;
+      }
+    }
+  }
+}
+
 // ----------------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

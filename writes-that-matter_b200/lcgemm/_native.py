@@ -46,6 +46,9 @@ SIGNATURES = {
     "lcg_gemm_r7_fused": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _i32,
                                  _vp, _vp]),
     "lcg_gemm_r7_fused_supported": (_i32, [_vp, _i64, _i64, _i64]),
+    "lcg_gemm_r7_ahead": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _i32, _i32,
+                                 _vp, _vp]),
+    "lcg_gemm_r7_ahead_scratch_bytes": (_i64, [_vp, _i64, _i64]),
     "lcg_gemm_r7_slab": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _i32,
                                 _i32, _i32, _i32, _vp, _vp]),
     "lcg_gate_up_chain": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,

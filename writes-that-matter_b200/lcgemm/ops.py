@@ -217,47 +217,110 @@ def gemm_r7_fused(a: torch.Tensor, b_pl: torch.Tensor, n: int, scheme, out: torc
     return out
 
 
+def ahead_scratch_bytes(scheme, m: int, k: int) -> int:
+    """Bytes of scratch :func:`gemm_r7_ahead` needs; -1 when it does not take the scheme / shape."""
+    return int(lib().lcg_gemm_r7_ahead_scratch_bytes(NativeScheme.of(scheme).handle, m, k))
+
+
+def gemm_r7_ahead(a: torch.Tensor, b_pl: torch.Tensor, n: int, scheme, out: torch.Tensor | None = None,
+                  scratch: torch.Tensor | None = None, schedule: int = nat.SCHEDULE_HYBRID,
+                  cta_group: int = 0, zero_out: bool = True) -> torch.Tensor:
+    """Bare rank-7 GEMM from the activation matrix with the A planes formed inside the GEMM
+    kernel, one product ahead of the MMAs (``lcg_gemm_r7_ahead``).  ``scratch`` is a byte tensor of
+    at least :func:`ahead_scratch_bytes`; it is allocated here when not given."""
+    _need(a, "activation"), _need(b_pl, "B planes")
+    m, k = a.shape
+    if tuple(b_pl.shape) != b_plane_shape(scheme, n, k):
+        raise ValueError(f"B planes must be {b_plane_shape(scheme, n, k)}, got {tuple(b_pl.shape)}")
+    need = ahead_scratch_bytes(scheme, m, k)
+    if need < 0:
+        raise ValueError("this scheme / shape has no in-kernel plane form (K % 128 != 0, or an A row "
+                         "with more than two terms)")
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.uint8, device=a.device)
+    if not scratch.is_cuda or scratch.dtype != torch.uint8 or scratch.numel() < need:
+        raise ValueError(f"scratch must be a CUDA uint8 tensor of at least {need} bytes")
+    if out is None:
+        out = _padded_out(m, n, a.device)
+    _need(out, "out")
+    if tuple(out.shape) != (m, n):
+        raise ValueError(f"out must be ({m}, {n}), got {tuple(out.shape)}")
+    if schedule == nat.SCHEDULE_RANK_SPLIT and zero_out:
+        out.zero_()
+    check(lib().lcg_gemm_r7_ahead(NativeScheme.of(scheme).handle, ptr(a), a.stride(0), ptr(b_pl),
+                                  b_pl.stride(0), ptr(out), out.stride(0), m, n, k, ptr(scratch),
+                                  scratch.numel(), schedule, cta_group, ptr(status_word(a.device)),
+                                  stream_ptr()))
+    return out
+
+
 def gemm_r7(a: torch.Tensor, b_pl: torch.Tensor, n: int, scheme, out: torch.Tensor | None = None,
             a_workspace: torch.Tensor | None = None, schedule: int = nat.SCHEDULE_HYBRID,
-            cta_group: int = 0, fused: bool | None = None) -> torch.Tensor:
-    """Bare rank-7 GEMM ``a (M, K) @ B^T`` with prepared B planes.
+            cta_group: int = 0, fused: bool | None = None, form: str | None = None,
+            scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """Bare rank-7 GEMM ``a (M, K) @ B^T`` with prepared B planes, in one of three forms:
 
-    ``fused=True`` forms the A operands inside the GEMM kernel (:func:`gemm_r7_fused`);
-    ``fused=False`` writes the A planes to ``a_workspace`` first and multiplies from there;
-    ``None`` picks by shape (:func:`prefers_fused_a`)."""
+    ``"planes"``  the A planes are written to ``a_workspace`` by a pass in front of the GEMM;
+    ``"ahead"``   the GEMM kernel's own plane warps form them, one product ahead of the MMAs,
+                  in ``scratch`` (:func:`gemm_r7_ahead`);
+    ``"fused"``   the A operand tiles are formed on their way into shared memory, nothing is
+                  written to global memory (:func:`gemm_r7_fused`; exact, but far slower: kept
+                  as the measured form of that data flow).
+
+    ``form=None`` picks ``"ahead"`` where the scheme and shape allow it and the output is narrow
+    (:func:`prefers_ahead`), else ``"planes"``.  ``fused=True / False`` is shorthand for
+    ``form="fused" / "planes"``."""
     m, k = a.shape
-    if fused is None:
-        fused = prefers_fused_a(scheme, m, n, k)
-    if fused:
+    if form is None:
+        if fused is not None:
+            form = "fused" if fused else "planes"
+        else:
+            form = "ahead" if prefers_ahead(scheme, m, n, k) else "planes"
+    if form == "fused":
         return gemm_r7_fused(a, b_pl, n, scheme, out=out, schedule=schedule, cta_group=cta_group)
+    if form == "ahead":
+        return gemm_r7_ahead(a, b_pl, n, scheme, out=out, scratch=scratch, schedule=schedule,
+                             cta_group=cta_group)
+    if form != "planes":
+        raise ValueError(f"unknown form {form!r}")
     planes = a_planes(a, scheme, out=a_workspace)
     return gemm_r7_planes(scheme, planes, b_pl, m, n, k, out=out, schedule=schedule,
                           cta_group=cta_group)
 
 
-# Output-column tiles (256 wide, per block column) up to which the fused A producer is the
-# faster form of the bare GEMM.  An A plane tile written once is re-read by every column tile, so
-# the plane pass amortises over wide outputs; over narrow ones it costs more than the 1/8 of the
-# products the decomposition saves, while the fused producer's cost is per MMA step.
-FUSED_A_MAX_TILES_N = 16
+# Output-column tiles (256 wide, per block column) up to which forming the A planes inside the
+# GEMM kernel beats the pass in front of it.  The pass costs the same whatever the output width
+# and so weighs most on narrow outputs; inside the kernel the plane warps' traffic shares each
+# SM's path to L2 with the operand stream, which the 256 x 256 x 64 pair tile already fills, so
+# the in-kernel form costs about half of what the separate pass costs and nothing less.
+AHEAD_MAX_TILES_N = 16
+_CTA_GROUPS = 74
 
 
-def bare_gemm_form(m: int, n: int, k: int):
-    """``(scheme name, fused)``: the form of the bare rank-7 GEMM an exact shape is dispatched
-    to.  Narrow outputs take the locality-ordered decomposition (one or two terms per A row)
-    with the A operands formed inside the kernel; wide ones take the postsum-CSE decomposition
-    (seven publications instead of twelve) on planes written by a pass in front."""
-    tiles_n = -(-((n + 1) // 2) // 256)
-    if k % 128 == 0 and k >= 128 and tiles_n <= FUSED_A_MAX_TILES_N:
-        return "2x2_locality_ordered", True
-    return "2x2_postsum_cse", False
+def prefers_ahead(scheme, m: int, n: int, k: int) -> bool:
+    if ahead_scratch_bytes(scheme, m, k) < 0:
+        return False
+    return -(-((n + 1) // 2) // 256) <= AHEAD_MAX_TILES_N
 
 
 def prefers_fused_a(scheme, m: int, n: int, k: int) -> bool:
-    if not fused_a_supported(scheme, m, n, k):
-        return False
-    tiles_n = -(-((n + 1) // 2) // 256)
-    return tiles_n <= FUSED_A_MAX_TILES_N
+    """The shared-memory form is never the fastest on this GPU (see :func:`gemm_r7`)."""
+    return False
+
+
+def bare_gemm_form(m: int, n: int, k: int):
+    """``(scheme name, form, schedule)``: what an exact shape of the bare rank-7 GEMM is
+    dispatched to.  Narrow outputs take the locality-ordered products with the two single-block
+    ones first and the in-kernel plane form; wide ones the postsum-CSE decomposition (seven
+    publications instead of twelve) on planes written by a pass in front.  The in-kernel form
+    runs the rank-split unit list when whole waves of tiles would leave a short last wave."""
+    tiles_m, tiles_n = -(-((m + 1) // 2) // 256), -(-((n + 1) // 2) // 256)
+    if k % 128 == 0 and k >= 128 and tiles_n <= AHEAD_MAX_TILES_N:
+        tiles = tiles_m * tiles_n
+        tail = tiles % _CTA_GROUPS
+        split = tiles >= 2 * _CTA_GROUPS and 0 < tail < _CTA_GROUPS // 4
+        return "2x2_locality_lead_single", "ahead", nat.SCHEDULE_RANK_SPLIT if split else nat.SCHEDULE_HYBRID
+    return "2x2_postsum_cse", "planes", nat.SCHEDULE_HYBRID
 
 
 def gate_up_chain(scheme, plane_scheme, a_pl, b_pl, z, down_planes, preclear=None,
