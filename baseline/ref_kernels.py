@@ -10,7 +10,12 @@ the reference's kernels pass a cluster mask to their TMA copies.  Prints one JSO
 a stage that fails to import, JIT-compile or run is reported with its error text instead of a
 time, and nothing is retried.
 
-    python baseline/ref_kernels.py TOKENS STEPS WARMUP
+    python baseline/ref_kernels.py TOKENS STEPS WARMUP [DUMP.pt]
+
+With DUMP.pt the kernels' outputs on the seeded inputs (residual stream, A planes, Z, the
+consumer's planes, the layer output) are saved there with torch.save, so that the caller can
+hold its own kernels' bits against them.  The inputs are bench.py's `make_layer_tensors`
+(seed 0) restated: x and the norm weight from one generator, the weights from a second.
 """
 import json
 import statistics
@@ -30,6 +35,7 @@ def main() -> None:
     tokens = int(sys.argv[1]) if len(sys.argv) > 1 else 2048
     steps = int(sys.argv[2]) if len(sys.argv) > 2 else 20
     warmup = int(sys.argv[3]) if len(sys.argv) > 3 else 3
+    dump = sys.argv[4] if len(sys.argv) > 4 else None
     hidden, inter, eps = 5120, 17408, 1e-6
     out = {"ref_kernels_child": True, "tokens": tokens, "hidden": hidden, "inter": inter,
            "steps": steps, "warmup": warmup, "stages": {}, "versions": {}}
@@ -59,8 +65,9 @@ def main() -> None:
     bf = torch.bfloat16
     x = torch.randn((tokens, hidden), generator=g, device=dev).to(bf)
     nw = (torch.randn((hidden,), generator=g, device=dev) * 0.01).to(bf)
-    wgu = (torch.randn((2 * inter, hidden), generator=g, device=dev) * 0.02).to(bf)
-    wd = (torch.randn((hidden, inter), generator=g, device=dev) * 0.02).to(bf)
+    gw = torch.Generator(device=dev).manual_seed(1000)
+    wgu = (torch.randn((2 * inter, hidden), generator=gw, device=dev) * 0.02).to(bf)
+    wd = (torch.randn((hidden, inter), generator=gw, device=dev) * 0.02).to(bf)
     zero = torch.zeros_like(x)
     flush = torch.empty(256 << 20, dtype=torch.int8, device=dev)
 
@@ -104,6 +111,18 @@ def main() -> None:
         except BaseException as exc:        # noqa: BLE001
             out["stages"][name] = {"unavailable": _short(exc)}
             break                            # later stages consume this one's output
+    if dump and all("mean_us" in out["stages"].get(k, {}) for k in ("norm_planes", "gate_up", "down")):
+        try:
+            gate.a_planes(x, zero, nw, eps)
+            gate.gemm(gate.a, gate_bw)
+            down.gemm(down.a_planes(), down_bw)
+            torch.cuda.synchronize()
+            torch.save({"residual_out": gate.residual_out.cpu(), "a_planes": gate.a.cpu(), "z": gate.c.cpu(),
+                        "planes": gate.planes.cpu(), "out": down.c.cpu(),
+                        "gate_bw": gate_bw[:4096].cpu(), "down_bw": down_bw[:4096].cpu()}, dump)
+            out["dump"] = dump
+        except BaseException as exc:        # noqa: BLE001
+            out["dump"] = "failed: " + _short(exc)
     try:
         out["describe"] = {"gate_up": gate.describe(), "down": down.describe()}
     except BaseException:                   # noqa: BLE001

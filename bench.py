@@ -175,10 +175,20 @@ def timed_steps(step_fn, steps, warmup, flush, sync_all, pre_step=None):
     return times
 
 
-def streamed_e2e_ms(layer, tokens, hidden, x_host, out_host, args, sync_all, group=None):
-    """ms per step of K host-to-host steps through HostStreamedLayer, one timed region."""
+def streamed_e2e_ms(layer, tokens, hidden, x_host, out_host, args, sync_all, group=None, timeline=None):
+    """ms per step of K host-to-host steps through HostStreamedLayer, one timed region.  With a
+    dict in `timeline`, a second, untimed run records per-step events on the three streams and
+    leaves their summary there."""
     from lcgemm.streaming import HostStreamedLayer
 
+    if timeline is not None:
+        tl = HostStreamedLayer(layer, tokens, hidden, group=group, timeline=True)
+        tl.begin()
+        for _ in range(max(8, args.steps)):
+            tl.submit(x_host, out_host)
+        tl.end()
+        timeline.update(tl.timeline_summary())
+        sync_all()
     st = HostStreamedLayer(layer, tokens, hidden, group=group)
 
     def run(k):
@@ -656,8 +666,10 @@ def run_ours(args, rank, world, device):
     x_slice = x_host[rank * rows:(rank + 1) * rows].clone().pin_memory()
     out_slice = torch.empty_like(x_slice).pin_memory()
     dist.barrier()
+    timeline = {}
     e2e_stream_ms = streamed_e2e_ms(layer, cfg["tokens"], cfg["hidden"], x_slice, out_slice, args,
-                                    sync_all, group=dist.group.WORLD)
+                                    sync_all, group=dist.group.WORLD, timeline=timeline)
+    phases = tp_phase_times(layer, x, args.steps, flush, sync_all) if args.exchange == "peer" else None
     t = torch.tensor([statistics.mean(times), e2e_stream_ms, statistics.mean(e2e_times)], device=device,
                      dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -680,7 +692,8 @@ def run_ours(args, rank, world, device):
                     "how": "lcgemm.streaming.HostStreamedLayer: each rank copies its tokens/tp rows of "
                            "the batch from pinned host memory (an all-gather over NVLink replicates "
                            "them) and its rows of the result back, copies overlapped with compute",
-                    "serial_ms_per_step": e2e_serial_ms},
+                    "serial_ms_per_step": e2e_serial_ms, "timeline_rank0": timeline},
+            "phases_ms": phases,
             "gpu_launches": launches * world,
             "roofline": {"bound": "tensor", "kernel": "whole step (per-rank rank-7 chain + exchange)",
                          "achieved": 0.875 * flops / (ms * 1e-3) / 1e12 / world, "peak": peak_burst,
@@ -801,6 +814,52 @@ def tp1_same_config(steps, warmup, flush, device):
     return {"ms_per_step": ms, "tflops": layer_flops(**TP) / (ms * 1e-3) / 1e12, **TP}
 
 
+def tp_phase_times(layer, x, steps, flush, sync_all):
+    """The fused tensor-parallel layer launched kernel by kernel with events between its phases:
+    mean ms per phase over `steps` cold-L2 steps, max over ranks.  (The timed headline replays
+    the same kernels as one CUDA graph, which removes the launch gaps these figures include.)"""
+    import torch.distributed as dist
+    from lcgemm import ops
+
+    lay, ex = layer.layer, layer.exchange
+    gate, down = lay.gate_plan, lay.down_plan
+    m, k, n = down.shape
+    zero = torch.zeros_like(x)
+    names = ("norm_planes", "gate_up", "down_push", "barrier_1", "reduce_gather", "barrier_2")
+    acc = {name: 0.0 for name in names}
+    for it in range(steps + 2):
+        flush.zero_()
+        dist.barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
+        b = ex.turn
+        ex.turn ^= 1
+        ev[0].record()
+        a = gate.a_planes(x, zero, lay.norm_weight, lay.eps)
+        ev[1].record()
+        gate.gemm(a, lay.gate_bw)
+        ev[2].record()
+        ops.gemm_r7_push(down.scheme, down.a_planes(), lay.down_bw, m, n, k, down.c, ex.slot_ptrs[b],
+                         ex.rank, ex.rows, cta_group=down.cta_group)
+        ev[3].record()
+        ex.barrier()
+        ev[4].record()
+        ops.reduce_gather(ex.slots[b], gate.residual_out, ex.out_ptrs, ex.rows, ex.rank)
+        ev[5].record()
+        ex.barrier()
+        ev[6].record()
+        ev[6].synchronize()
+        if it >= 2:
+            for j, name in enumerate(names):
+                acc[name] += ev[j].elapsed_time(ev[j + 1])
+    sync_all()
+    ops.check_status()
+    t = torch.tensor([acc[name] / steps for name in names], device=x.device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    out = dict(zip(names, t.tolist()))
+    out["sum"] = sum(out.values())
+    return out
+
+
 def tp_parity(fused_layer, x, nw, wgu, wd, cfg, rank, world, device):
     """Checked before anything is timed: the fused exchange's output against the same layer
     with one NCCL all-reduce, against a dense cuBLAS evaluation of a row sample (each rank its
@@ -862,8 +921,16 @@ def run_case(args, device):
     from lcgemm import ops, scheme as S
     from lcgemm.seams import build_chain
 
-    m, h, i = args.tokens, SINGLE["hidden"], SINGLE["inter"]
+    m, h, i = args.tokens, args.hidden, args.inter
     flush = torch.empty(FLUSH_BYTES, dtype=torch.int8, device=device)
+    if args.case == "layer":
+        # the whole layer in its three arms at any (tokens, hidden, intermediate), e.g. the
+        # reference's second model family: --hidden 6656 --inter 19968
+        res = bench_layer_arms(m, h, i, args.steps, args.warmup, flush, device, graphs=args.graphs)
+        res.pop("objects"), res.pop("arms")
+        print(json.dumps({"case": "layer", "tokens": m, "hidden": h, "inter": i, "steps": args.steps,
+                          "warmup": args.warmup, **_arm_summary(res, layer_flops(m, h, i))}))
+        return
     x, nw, wgu, wd = make_layer_tensors(m, h, i, device)
     gate, down = build_chain((m, h, 2 * i), (m, i, h))
     zero = torch.zeros_like(x)
@@ -967,6 +1034,43 @@ def run_sweep(args, device):
             torch.cuda.empty_cache()
 
 
+def _compare_with_reference_kernels(d, gate, down, gate_bw, down_bw, x, zero, nw):
+    """This library's kernels against the outputs the reference's kernels left for the same seeded
+    inputs: each of ours is fed the REFERENCE's output of the stage before it, so that a
+    difference belongs to one kernel.  gate_up runs the all-ranks schedule here (one writer per C
+    block, fixed order: the reference's schedule for this shape)."""
+    from lcgemm import ops
+    from lcgemm._native import SCHEDULE_ALL_RANKS
+
+    dev = x.device
+    mism = lambda a, b: float((a.view(torch.int16) != b.view(torch.int16)).float().mean().item())
+    rel = lambda a, b: float(((a.float() - b.float()).norm() / b.float().norm()).item())
+    ref = {k: v.to(dev) for k, v in d.items()}
+    out = {"b_planes_equal": bool(torch.equal(gate_bw[:4096], ref["gate_bw"])
+                                  and torch.equal(down_bw[:4096], ref["down_bw"]))}
+    a = gate.a_planes(x, zero, nw, EPS)
+    out["residual_out_equal"] = bool(torch.equal(gate.residual_out, ref["residual_out"]))
+    out["a_planes_mismatch_fraction"] = mism(a, ref["a_planes"])
+    out["a_planes_rel"] = rel(a, ref["a_planes"])
+    saved = gate.schedule
+    gate.schedule = SCHEDULE_ALL_RANKS
+    try:
+        z = gate.gemm(ref["a_planes"], gate_bw)
+        out["z_equal_given_reference_a_planes"] = bool(torch.equal(z, ref["z"]))
+        out["z_mismatch_fraction"] = mism(z, ref["z"])
+        out["down_planes_equal"] = bool(torch.equal(gate.planes, ref["planes"]))
+        out["down_planes_mismatch_fraction"] = mism(gate.planes, ref["planes"])
+    finally:
+        gate.schedule = saved
+    z_h = gate.gemm(ref["a_planes"], gate_bw)
+    out["z_rel_hybrid_schedule"] = rel(z_h, ref["z"])
+    o = down.gemm(ref["planes"], down_bw)
+    out["out_rel_given_reference_planes"] = rel(o, ref["out"])
+    out["out_mismatch_fraction"] = mism(o, ref["out"])
+    ops.check_status()
+    return out
+
+
 def run_ref_kernels(args, device):
     """The reference's own sm_100 kernels beside this library's, same GPU, same call: the fused
     norm + A-plane kernel, the chained gate_up GEMM and the rank-split down GEMM of one layer at
@@ -1002,8 +1106,11 @@ def run_ref_kernels(args, device):
     torch.cuda.synchronize()
     child = ROOT / "baseline" / "ref_kernels.py"
     ref = None
+    import tempfile
+
+    dump = Path(tempfile.gettempdir()) / f"lcg_ref_kernels_{os.getpid()}.pt"
     try:
-        proc = subprocess.run([sys.executable, str(child), str(m), str(args.steps), str(args.warmup)],
+        proc = subprocess.run([sys.executable, str(child), str(m), str(args.steps), str(args.warmup), str(dump)],
                               capture_output=True, text=True, timeout=args.ref_timeout)
         for ln in reversed(proc.stdout.strip().splitlines()):
             if ln.startswith("{"):
@@ -1015,9 +1122,16 @@ def run_ref_kernels(args, device):
     except subprocess.TimeoutExpired:
         ref = {"unavailable": f"child did not finish within {args.ref_timeout} s"}
     after = ours()
+    bits = None
+    if dump.exists():
+        try:
+            bits = _compare_with_reference_kernels(torch.load(dump), gate, down, gate_bw, down_bw, x, zero, nw)
+        finally:
+            dump.unlink()
     print(json.dumps({"ref_kernels": True, "tokens": m, "hidden": h, "inter": i, "steps": args.steps,
                       "warmup": args.warmup, "l2": "flushed between timed launches",
                       "ours_before": before, "reference": ref, "ours_after": after,
+                      "bits_vs_reference_kernels": bits,
                       "describe": {"gate_up": gate.describe(), "down": down.describe()}}))
 
 
@@ -1186,8 +1300,11 @@ def main():
     ap.add_argument("--prompts", type=int, default=8, help="seeded prompts per length for --model's agreement rates")
     ap.add_argument("--model-tokens", default="2048,4096,8192", help="prompt lengths for --model")
     ap.add_argument("--case", default=None,
-                    help="time one kernel alone: gate_up | down | norm_planes | a_planes | dense_gate_up")
+                    help="time one kernel alone: gate_up | down | norm_planes | a_planes | dense_gate_up; "
+                         "or `layer`: the whole layer's three arms at --tokens / --hidden / --inter")
     ap.add_argument("--tokens", type=int, default=4096, help="token count for --case")
+    ap.add_argument("--hidden", type=int, default=SINGLE["hidden"], help="hidden size for --case")
+    ap.add_argument("--inter", type=int, default=SINGLE["inter"], help="intermediate size for --case")
     ap.add_argument("--sweep", action="store_true", help="bare-GEMM shape sweep, odd shapes included")
     ap.add_argument("--sweep-fused", action="store_true",
                     help="--sweep: also time the form that builds the A operand tiles in shared memory (slow)")

@@ -27,7 +27,8 @@ class HostStreamedLayer:
     ``(tokens / tp, hidden)`` of the batch and of the result (``tokens`` must divide).
     """
 
-    def __init__(self, layer, tokens: int, hidden: int, device=None, group=None, depth: int = 2):
+    def __init__(self, layer, tokens: int, hidden: int, device=None, group=None, depth: int = 2,
+                 timeline: bool = False):
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.layer, self.depth, self.group = layer, depth, group
         self.world = dist.get_world_size(group) if (group is not None or (
@@ -45,6 +46,10 @@ class HostStreamedLayer:
         mk = lambda: [torch.cuda.Event() for _ in range(depth)]
         self.x_ready, self.x_free, self.out_ready, self.out_free = mk(), mk(), mk(), mk()
         self.n = 0
+        # With `timeline`, every step records timed events at the start and end of its copy in,
+        # its compute (all-gather + layer + slice copy) and its copy out; `timeline_summary`
+        # turns them into durations and the overlap between neighbouring steps.
+        self.timeline = [] if timeline else None
 
     def begin(self) -> None:
         """Order the copy streams after what is already queued on the current stream."""
@@ -59,24 +64,45 @@ class HostStreamedLayer:
         compute = torch.cuda.current_stream()
         if not first_use:
             self.s_in.wait_event(self.x_free[i])          # the batch that used this buffer is done
+        ev = None
+        if self.timeline is not None:
+            ev = {k: torch.cuda.Event(enable_timing=True) for k in
+                  ("in0", "in1", "c0", "gathered", "c1", "out0", "out1")}
+            self.timeline.append(ev)
         with torch.cuda.stream(self.s_in):
+            if ev:
+                ev["in0"].record()
             self.x_in[i].copy_(x_host, non_blocking=True)
+            if ev:
+                ev["in1"].record()
             self.x_ready[i].record()
         compute.wait_event(self.x_ready[i])
+        if ev:
+            ev["c0"].record(compute)
         if self.world > 1:
             dist.all_gather_into_tensor(self.x_dev[i], self.x_in[i], group=self.group)
+        if ev:
+            ev["gathered"].record(compute)
         out = self.layer(self.x_dev[i])
         self.x_free[i].record(compute)
         if out_host is None:
+            if ev:
+                ev["c1"].record(compute)
             return
         if not first_use:
             compute.wait_event(self.out_free[i])          # its previous content has left the GPU
         r0 = self.rank * self.rows
         self.out_dev[i].copy_(out[r0:r0 + self.rows])
         self.out_ready[i].record(compute)
+        if ev:
+            ev["c1"].record(compute)
         self.s_out.wait_event(self.out_ready[i])
         with torch.cuda.stream(self.s_out):
+            if ev:
+                ev["out0"].record()
             out_host.copy_(self.out_dev[i], non_blocking=True)
+            if ev:
+                ev["out1"].record()
             self.out_free[i].record()
 
     def end(self) -> None:
@@ -86,6 +112,24 @@ class HostStreamedLayer:
             ev = torch.cuda.Event()
             ev.record(s)
             cur.wait_event(ev)
+
+    def timeline_summary(self, skip: int = 2) -> dict:
+        """Mean durations (ms) over the recorded steps after the first `skip`: copy in, all-gather,
+        layer + slice copy, copy out, the period between the starts of neighbouring steps' compute,
+        and how long the compute stream sat idle between one step's end and the next one's start."""
+        if not self.timeline:
+            return {}
+        self.drain()
+        steps = [e for e in self.timeline[skip:] if "out1" in e]
+        if len(steps) < 2:
+            return {}
+        mean = lambda v: sum(v) / len(v)
+        dur = lambda a, b: mean([e[a].elapsed_time(e[b]) for e in steps])
+        period = mean([steps[j]["c0"].elapsed_time(steps[j + 1]["c0"]) for j in range(len(steps) - 1)])
+        idle = mean([steps[j]["c1"].elapsed_time(steps[j + 1]["c0"]) for j in range(len(steps) - 1)])
+        return {"steps": len(steps), "h2d_ms": dur("in0", "in1"), "all_gather_ms": dur("c0", "gathered"),
+                "layer_ms": dur("gathered", "c1"), "d2h_ms": dur("out0", "out1"),
+                "compute_period_ms": period, "compute_idle_ms": idle}
 
     def drain(self) -> None:
         """Wait for everything queued and raise if a device-side wait ran out on the way (under
