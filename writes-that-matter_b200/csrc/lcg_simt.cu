@@ -332,6 +332,107 @@ k_norm_planes_staged(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat1
   }
 }
 
+// The same seam with everything in registers, for rows of at most 416 vectors per block column
+// (K <= 6656): one thread owns vector v of all four blocks of the row pair.  All eight loads of a
+// thread are issued before anything is consumed (they are its whole share of the memory-level
+// parallelism), the rounded sum h stays in registers as bf16, and the residual stream is stored
+// before the barrier so that it streams out while the CTA waits there
+// (lcgemm/kernels/fused_norm.py:166-198).  Two CTAs to an SM.
+__device__ __forceinline__ Vec8 ldg_stream(const __nv_bfloat16* p) {
+  const uint4 q = __ldcs(reinterpret_cast<const uint4*>(p));
+  return *reinterpret_cast<const Vec8*>(&q);
+}
+__device__ __forceinline__ void stg_stream(__nv_bfloat16* p, const Vec8& v) {
+  __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(&v));
+}
+
+template <unsigned long long kCode>      // the packed A table (compile time only)
+__global__ void __launch_bounds__(416, 2)
+k_norm_planes_reg(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __restrict__ residual,
+                  const __nv_bfloat16* __restrict__ norm_w, int m2, int k, float eps,
+                  __nv_bfloat16* residual_out, __nv_bfloat16* __restrict__ out, int ld_out) {
+  __shared__ float s_part[2][16];
+  const int rho = blockIdx.x;
+  const int k2 = k / 2;
+  const int nvec = k2 / 8;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const bool live = tid < nvec;
+  const int v = live ? tid : 0;
+
+  Vec8 d[2][2], r[2][2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+      const size_t off = (static_cast<size_t>(i) * m2 + rho) * k + kb * k2 + v * 8;
+      d[i][kb] = ldg_stream(delta + off);
+      r[i][kb] = ldg_stream(residual + off);
+    }
+  float w[2][8];
+#pragma unroll
+  for (int kb = 0; kb < 2; ++kb) {
+    unpack8(*reinterpret_cast<const Vec8*>(norm_w + kb * k2 + v * 8), w[kb]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) w[kb][e] += 1.0f;
+  }
+  Vec8 h[2][2];
+  float ss[2] = {0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+      float df[8], rf[8], sf[8];
+      unpack8(d[i][kb], df);
+      unpack8(r[i][kb], rf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sf[e] = df[e] + rf[e];
+      h[i][kb] = pack8(sf);               // the norm sees exactly what is stored as the residual
+      if (live)
+        stg_stream(residual_out + (static_cast<size_t>(i) * m2 + rho) * k + kb * k2 + v * 8, h[i][kb]);
+      float hf[8];
+      unpack8(h[i][kb], hf);
+      if (live) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss[i] = fmaf(hf[e], hf[e], ss[i]);
+      }
+    }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], o);
+    if (lane == 0) s_part[i][warp] = ss[i];
+  }
+  __syncthreads();
+  float rstd[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float part = lane < nwarps ? s_part[i][lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    rstd[i] = rsqrtf(part / static_cast<float>(k) + eps);
+  }
+  if (!live) return;
+  float y[4][8];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+      float hf[8];
+      unpack8(h[i][kb], hf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[i * 2 + kb][e] = hf[e] * rstd[i] * w[kb][e];
+    }
+  __nv_bfloat16* dst = out + static_cast<size_t>(rho) * ld_out + v * 8;
+  const size_t plane_stride = static_cast<size_t>(m2) * ld_out;
+#pragma unroll
+  for (int rr = 0; rr < kMaxRank; ++rr) {
+    float o[8];
+    signed_sum_fixed<kCode>(rr, y, o);
+    stg_stream(dst + rr * plane_stride, pack8(o));
+  }
+}
+
 // --------------------------------------------------------- SwiGLU + planes
 __device__ __forceinline__ float silu_f32(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
@@ -515,6 +616,23 @@ extern "C" int lcg_norm_planes(const lcg_scheme_t* scheme, const void* delta, co
     return fail(LCG_ERR_BAD_ARG, "plane leading dimension %lld must be >= %lld and a multiple of 8",
                 (long long)ld_out, (long long)k2p);
   const int64_t nvec_p = k2p / 8;
+  // Register form: a shipped table and rows of at most 416 vectors per block column.
+  if (k2p == K / 2 && K / 16 <= 416 && M / 2 <= 0x7fffffff && ld_out <= 0x7fffffff) {
+    const TermTable table = a_table(scheme);
+    const unsigned long long code = table_code(table, scheme->rank);
+    if (code == kCodePostsumA || code == kCodeLocalityA) {
+      const int nvec = static_cast<int>(K / 16);
+      const int threads = (nvec + 31) / 32 * 32;
+      auto kern = code == kCodePostsumA ? k_norm_planes_reg<kCodePostsumA> : k_norm_planes_reg<kCodeLocalityA>;
+      kern<<<static_cast<unsigned>(M / 2), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+          static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(residual),
+          static_cast<const __nv_bfloat16*>(norm_weight), static_cast<int>(M / 2), static_cast<int>(K), eps,
+          static_cast<__nv_bfloat16*>(residual_out), static_cast<__nv_bfloat16*>(out), static_cast<int>(ld_out));
+      LCG_CUDA_OK(cudaGetLastError());
+      count_launch();
+      return LCG_OK;
+    }
+  }
   // Staged form: whole row pair in shared memory, when it fits three CTAs to an SM.
   if (k2p == K / 2 && 8 * K <= 72 * 1024 && M / 2 <= 0x7fffffff && ld_out <= 0x7fffffff) {
     const int nvec = static_cast<int>(K / 16);
