@@ -96,7 +96,9 @@ def test_two_gpu_tensor_parallel_layer():
              fused_branch, ranks_equal, captured_branch) = ret[rank]
             # the MLP branch (output minus residual) is ~9 % of the output here, so the bounds on
             # the whole output are loose on the branch; these are on the branch itself
-            assert fused_branch < 1.5e-2, (rank, fused_branch)   # fp32 sum of partials vs bf16 all-reduce
+            # (both outputs are rounded to bf16 at the residual's magnitude, which alone is ~1.5 % of
+            # this branch; the whole-output bound above allows 4-5 %)
+            assert fused_branch < 2.5e-2, (rank, fused_branch)   # fp32 sum of partials vs bf16 all-reduce
             assert ranks_equal, rank                              # all ranks hold identical bits
             # graph replay vs eager launches of the same kernels: the split tail of the push GEMM adds
             # into C in an order the hardware picks, so equal up to that, not bit for bit
