@@ -65,8 +65,10 @@ def test_apply_terms_signed_sum():
 
 
 def test_rank_split_rule():
-    for shape in down_seam.RANK_SPLIT_SHAPES:
+    for shape in down_seam.RANK_SPLIT_SHAPES - down_seam.HYBRID_SHAPES:
         assert down_seam.wants_rank_split(shape)
+    for shape in down_seam.HYBRID_SHAPES:                          # measured exceptions
+        assert not down_seam.wants_rank_split(shape)
     assert down_seam.wants_rank_split((8192, 3584, 8192))          # TP8 down: 256 tiles on 74 groups
     assert not down_seam.wants_rank_split((8192, 5120, 37888))      # 16 x 74 tiles: whole waves
 

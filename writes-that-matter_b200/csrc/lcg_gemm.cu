@@ -954,7 +954,7 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
 }
 
 // Zero the C blocks of the tail tiles of a hybrid launch (their products arrive as
-// reduce-adds from several CTAs).  grid = (tail tiles, 4 blocks), 256 threads.
+// reduce-adds from several CTAs).  grid = (tail tiles, 4 blocks, 4 row quarters), 256 threads.
 struct ZeroArgs {
   __nv_bfloat16* c;
   int64_t ldc;
@@ -967,11 +967,13 @@ k_zero_tail_tiles(const __grid_constant__ GemmParams p, const ZeroArgs z) {
   const int bi = blockIdx.y >> 1, bj = blockIdx.y & 1;
   const int rows = bi == 0 ? z.m2 : z.m - z.m2;
   const int cols = bj == 0 ? z.n2 : z.n - z.n2;
-  const int r1 = min(tm * z.tile_m + z.tile_m, rows);
+  const int quarter = z.tile_m / 4;
+  const int r0 = tm * z.tile_m + static_cast<int>(blockIdx.z) * quarter;
+  const int r1 = min(r0 + quarter, rows);
   const int c1 = min(tn * kBN + kBN, cols);
   __nv_bfloat16* base = z.c + static_cast<int64_t>(bi) * z.m2 * z.ldc + static_cast<int64_t>(bj) * z.n2;
   const int col = tn * kBN + (threadIdx.x & 31) * 8;
-  for (int row = tm * z.tile_m + (threadIdx.x >> 5); row < r1; row += 8) {
+  for (int row = r0 + (threadIdx.x >> 5); row < r1; row += 8) {
     __nv_bfloat16* ptr = base + static_cast<int64_t>(row) * z.ldc + col;
     if (col + 8 <= c1) {
       *reinterpret_cast<uint4*>(ptr) = make_uint4(0u, 0u, 0u, 0u);
@@ -1233,7 +1235,7 @@ int zero_tail_tiles(const GemmParams& p, void* c, int64_t ldc, int64_t M, int64_
   z.m2 = static_cast<int32_t>(g.m2);
   z.n2 = static_cast<int32_t>(g.n2);
   z.tile_m = kBM * cta_group;
-  k_zero_tail_tiles<<<dim3(static_cast<unsigned>(p.tail_tiles), 4), 256, 0, stream>>>(p, z);
+  k_zero_tail_tiles<<<dim3(static_cast<unsigned>(p.tail_tiles), 4, 4), 256, 0, stream>>>(p, z);
   LCG_CUDA_OK(cudaGetLastError());
   count_launch();
   return LCG_OK;

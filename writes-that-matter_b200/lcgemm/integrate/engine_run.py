@@ -27,20 +27,31 @@ os.environ["VLLM_ENABLE_V1_MULTIPROCESSING"] = "0"     # in-process engine: plan
 
 
 def write_config(directory: Path, layers: int, tokens: int) -> Path:
+    """A Qwen3.5-style config: the installed vLLM builds this model family from the combined
+    (vision + text) config and runs it with ``language_model_only=True``, as the reference's
+    harness does (``lcgemm/bench/prefill.py:60-68,104-106``); the vision tower is kept minimal."""
     pattern = ["linear_attention", "linear_attention", "linear_attention", "full_attention"]
-    cfg = {
-        "architectures": ["Qwen3_5ForCausalLM"], "model_type": "qwen3_5_text",
+    text = {
+        "model_type": "qwen3_5_text",
         "hidden_size": 5120, "intermediate_size": 17408, "num_hidden_layers": layers,
         "num_attention_heads": 24, "num_key_value_heads": 4, "head_dim": 256,
         "linear_conv_kernel_dim": 4, "linear_key_head_dim": 128, "linear_value_head_dim": 128,
         "linear_num_key_heads": 16, "linear_num_value_heads": 48,
         "layer_types": [pattern[i % 4] for i in range(layers)], "full_attention_interval": 4,
         "vocab_size": 151936, "max_position_embeddings": max(8192, tokens) + 512, "rms_norm_eps": 1e-6,
-        "hidden_act": "silu", "tie_word_embeddings": False, "torch_dtype": "bfloat16",
-        "attention_bias": False, "attention_dropout": 0.0, "partial_rotary_factor": 0.25,
-        "rope_parameters": {"rope_type": "default", "rope_theta": 10000000.0, "partial_rotary_factor": 0.25},
-        "bos_token_id": 1, "eos_token_id": 2,
+        "hidden_act": "silu", "tie_word_embeddings": False, "attention_bias": False,
+        "attention_dropout": 0.0, "partial_rotary_factor": 0.25,
+        "rope_parameters": {"rope_type": "default", "rope_theta": 10000000.0, "partial_rotary_factor": 0.25,
+                            "mrope_section": [11, 11, 10], "mrope_interleaved": True},
+        "bos_token_id": 1, "eos_token_id": 2, "dtype": "bfloat16",
     }
+    vision = {"model_type": "qwen3_5", "depth": 1, "hidden_size": 128, "intermediate_size": 256, "num_heads": 2,
+              "out_hidden_size": 5120, "num_position_embeddings": 64, "patch_size": 16,
+              "spatial_merge_size": 2, "temporal_patch_size": 2, "in_channels": 3}
+    cfg = {"architectures": ["Qwen3_5ForConditionalGeneration"], "model_type": "qwen3_5",
+           "text_config": text, "vision_config": vision, "tie_word_embeddings": False,
+           "image_token_id": 151655, "video_token_id": 151656, "vision_start_token_id": 151652,
+           "vision_end_token_id": 151653, "torch_dtype": "bfloat16"}
     directory.mkdir(parents=True, exist_ok=True)
     (directory / "config.json").write_text(json.dumps(cfg, indent=1))
     return directory
@@ -63,7 +74,7 @@ def run_arm(args) -> dict:
     llm = LLM(model=str(model_dir), load_format="dummy", skip_tokenizer_init=True,
               max_model_len=args.tokens + 256, max_num_batched_tokens=args.tokens + 256, max_num_seqs=1,
               gpu_memory_utilization=args.gpu_memory_utilization, enable_prefix_caching=False,
-              dtype="bfloat16", enforce_eager=args.enforce_eager, seed=0)
+              dtype="bfloat16", enforce_eager=args.enforce_eager, seed=0, language_model_only=True)
     build_s = time.perf_counter() - t0
     info = patch.install(llm, tokens=args.tokens) if patch else {}
     prompt = TokensPrompt(prompt_token_ids=[1000 + i % 5000 for i in range(args.tokens)])

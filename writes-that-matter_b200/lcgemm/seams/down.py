@@ -14,7 +14,7 @@ import math
 import torch
 
 from .. import chain_gauge, ops
-from .._native import SCHEDULE_ALL_RANKS, SCHEDULE_RANK_SPLIT
+from .._native import SCHEDULE_ALL_RANKS, SCHEDULE_HYBRID, SCHEDULE_RANK_SPLIT
 from ..scheme import Scheme
 
 # Shapes the reference runs rank-split (lcgemm/seams/down.py:42-54); kept as the validated set.
@@ -23,6 +23,10 @@ RANK_SPLIT_SHAPES = {
     (2048, 19968, 6656), (2048, 17408, 5120), (4096, 17408, 5120), (8192, 17408, 5120),
 }
 
+# Measured exceptions to the rank-split rule: whole waves of tiles walked product by product with
+# only the last partial wave split (8192 tokens: 867 us against 888 us rank-split, chained).
+HYBRID_SHAPES = {(8192, 17408, 5120)}
+
 _CTA_GROUPS = 74            # 2-CTA groups resident on a 148-SM B200
 _SPLIT_PENALTY = 0.97       # reduce-add scatter and pre-zeroing cost of the rank-split form
 
@@ -30,6 +34,8 @@ _SPLIT_PENALTY = 0.97       # reduce-add scatter and pre-zeroing cost of the ran
 def wants_rank_split(shape) -> bool:
     """Whether the product index has to carry parallelism: compare the wave-quantisation
     efficiency of ``tiles`` units against ``7 * tiles`` units on the resident CTA groups."""
+    if tuple(shape) in HYBRID_SHAPES:
+        return False
     if tuple(shape) in RANK_SPLIT_SHAPES:
         return True
     m, _, n = shape
@@ -54,8 +60,21 @@ class DownPlan:
         dev = torch.device("cuda", torch.cuda.current_device())
         self._store = torch.empty((m, (n + 7) // 8 * 8), device=dev, dtype=torch.bfloat16)
         self.c = self._store[:, :n] if n % 8 else self._store
-        self.rank_split = wants_rank_split(self.shape)
+        if wants_rank_split(self.shape):
+            self.schedule = SCHEDULE_RANK_SPLIT
+        else:
+            self.schedule = SCHEDULE_HYBRID if self.shape in HYBRID_SHAPES else SCHEDULE_ALL_RANKS
         self._desc = None
+
+    @property
+    def rank_split(self) -> bool:
+        """Whether every contribution is a reduce-add into an output that must arrive zeroed
+        (``lcgemm/seams/down.py:67-68`` of the reference)."""
+        return self.schedule == SCHEDULE_RANK_SPLIT
+
+    @rank_split.setter
+    def rank_split(self, value: bool) -> None:
+        self.schedule = SCHEDULE_RANK_SPLIT if value else SCHEDULE_ALL_RANKS
 
     # ---------------------------------------------------------------- offline
     def prepare_weight(self, w: torch.Tensor) -> torch.Tensor:
@@ -75,8 +94,7 @@ class DownPlan:
         cleared_by_producer = (self.producer is not None and c is self.c
                                and getattr(self.producer, "preclear", None) is self.c)
         ops.gemm_r7_planes(
-            self.scheme, a_planes, prepared_w, m, n, k, out=c,
-            schedule=SCHEDULE_RANK_SPLIT if self.rank_split else SCHEDULE_ALL_RANKS,
+            self.scheme, a_planes, prepared_w, m, n, k, out=c, schedule=self.schedule,
             cta_group=self.cta_group, zero_out=self.rank_split and not cleared_by_producer)
         return c
 
@@ -101,8 +119,7 @@ class DownPlan:
         all-reduce of the previous slab."""
         m, k, n = self.shape
         ops.gemm_r7_slab(self.scheme, a_planes, prepared_w, m, n, k, self.c, tile_range,
-                         schedule=SCHEDULE_RANK_SPLIT if self.rank_split else SCHEDULE_ALL_RANKS,
-                         max_groups=max_groups, cta_group=2)
+                         schedule=self.schedule, max_groups=max_groups, cta_group=2)
         return self.c
 
     def __call__(self, *, prepared_w, out=None):
@@ -112,6 +129,5 @@ class DownPlan:
         if self._desc is None:
             m, k, n = self.shape
             self._desc = "  chained (a_planes are free)\n" + ops.describe_gemm(
-                m, n, k, True, SCHEDULE_RANK_SPLIT if self.rank_split else SCHEDULE_ALL_RANKS,
-                self.cta_group)
+                m, n, k, True, self.schedule, self.cta_group)
         return self._desc
