@@ -10,7 +10,7 @@ the reference's kernels pass a cluster mask to their TMA copies.  Prints one JSO
 a stage that fails to import, JIT-compile or run is reported with its error text instead of a
 time, and nothing is retried.
 
-    python baseline/ref_kernels.py TOKENS STEPS WARMUP [DUMP.pt]
+    python baseline/ref_kernels.py TOKENS STEPS WARMUP [DUMP.pt|-] [HIDDEN INTER]
 
 With DUMP.pt the kernels' outputs on the seeded inputs (residual stream, A planes, Z, the
 consumer's planes, the layer output) are saved there with torch.save, so that the caller can
@@ -35,8 +35,10 @@ def main() -> None:
     tokens = int(sys.argv[1]) if len(sys.argv) > 1 else 2048
     steps = int(sys.argv[2]) if len(sys.argv) > 2 else 20
     warmup = int(sys.argv[3]) if len(sys.argv) > 3 else 3
-    dump = sys.argv[4] if len(sys.argv) > 4 else None
-    hidden, inter, eps = 5120, 17408, 1e-6
+    dump = sys.argv[4] if len(sys.argv) > 4 and sys.argv[4] != "-" else None
+    hidden = int(sys.argv[5]) if len(sys.argv) > 5 else 5120
+    inter = int(sys.argv[6]) if len(sys.argv) > 6 else 17408
+    eps = 1e-6
     out = {"ref_kernels_child": True, "tokens": tokens, "hidden": hidden, "inter": inter,
            "steps": steps, "warmup": warmup, "stages": {}, "versions": {}}
     if not (REF / "lcgemm").is_dir():

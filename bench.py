@@ -951,6 +951,14 @@ def run_case(args, device):
         s_tok = torch.randn((m, i), device=device).to(torch.bfloat16)       # a down-shaped activation
         ws = torch.empty(ops.a_plane_shape(down.scheme, m, i), device=device, dtype=torch.bfloat16)
         fn, flops = (lambda: ops.a_planes(s_tok, down.scheme, out=ws)), 0.0
+    elif args.case == "bare_ahead":
+        # the down-shaped bare GEMM with its A planes formed inside the kernel, one product ahead
+        lead = S.load("2x2_locality_lead_single")
+        s_tok = torch.randn((m, i), device=device).to(torch.bfloat16)
+        bp = ops.prepare_b(wd, lead)
+        scr = torch.empty(ops.ahead_scratch_bytes(lead, m, i), dtype=torch.uint8, device=device)
+        out = torch.empty((m, h), device=device, dtype=torch.bfloat16)
+        fn, flops = (lambda: ops.gemm_r7_ahead(s_tok, bp, h, lead, out=out, scratch=scr)), 2.0 * m * i * h
     elif args.case == "dense_gate_up":
         out = torch.empty((m, 2 * i), device=device, dtype=torch.bfloat16)
         fn, flops = (lambda: ops.gemm_dense(x, wgu, out=out)), 2.0 * m * h * 2 * i
@@ -1084,7 +1092,7 @@ def run_ref_kernels(args, device):
     from lcgemm import ops
     from lcgemm.seams import build_chain
 
-    m, h, i = args.tokens, SINGLE["hidden"], SINGLE["inter"]
+    m, h, i = args.tokens, args.hidden, args.inter
     flush = torch.empty(FLUSH_BYTES, dtype=torch.int8, device=device)
     x, nw, wgu, wd = make_layer_tensors(m, h, i, device)
     gate, down = build_chain((m, h, 2 * i), (m, i, h))
@@ -1112,8 +1120,8 @@ def run_ref_kernels(args, device):
 
     dump = Path(tempfile.gettempdir()) / f"lcg_ref_kernels_{os.getpid()}.pt"
     try:
-        proc = subprocess.run([sys.executable, str(child), str(m), str(args.steps), str(args.warmup), str(dump)],
-                              capture_output=True, text=True, timeout=args.ref_timeout)
+        proc = subprocess.run([sys.executable, str(child), str(m), str(args.steps), str(args.warmup), str(dump),
+                               str(h), str(i)], capture_output=True, text=True, timeout=args.ref_timeout)
         for ln in reversed(proc.stdout.strip().splitlines()):
             if ln.startswith("{"):
                 ref = json.loads(ln)
@@ -1302,7 +1310,7 @@ def main():
     ap.add_argument("--prompts", type=int, default=8, help="seeded prompts per length for --model's agreement rates")
     ap.add_argument("--model-tokens", default="2048,4096,8192", help="prompt lengths for --model")
     ap.add_argument("--case", default=None,
-                    help="time one kernel alone: gate_up | down | norm_planes | a_planes | dense_gate_up; "
+                    help="time one kernel alone: gate_up | down | norm_planes | a_planes | bare_ahead | dense_gate_up; "
                          "or `layer`: the whole layer's three arms at --tokens / --hidden / --inter")
     ap.add_argument("--tokens", type=int, default=4096, help="token count for --case")
     ap.add_argument("--hidden", type=int, default=SINGLE["hidden"], help="hidden size for --case")
