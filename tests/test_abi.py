@@ -28,7 +28,7 @@ def test_version_and_error_text(native_lib):
     assert isinstance(native_lib.lcg_last_error(), bytes)
 
 
-@pytest.mark.parametrize("name", ["2x2_postsum_cse", "2x2_locality_ordered"])
+@pytest.mark.parametrize("name", ["2x2_postsum_cse", "2x2_locality_ordered", "2x2_locality_lead_single"])
 def test_native_plan_equals_host_plan(native_lib, name):
     s = S.load(name)
     native = nat.NativeScheme(s).plan()
@@ -83,3 +83,31 @@ def test_describe_and_argument_checks_do_not_need_a_gpu(native_lib):
     assert native_lib.lcg_gemm_r7(sch, fake, 64, fake, 64, fake, 64, 64, 64, 128, 5, 0, None,
                                   None) == nat.ERR_BAD_ARG
     assert native_lib.lcg_launch_count() == 0
+
+
+def test_in_kernel_plane_forms_say_what_they_take(native_lib):
+    """Host-side answers of the two entry points that form A operands inside the GEMM kernel
+    (no launch): which schemes and shapes they take, how much scratch the product-ahead form
+    needs, and that bad arguments are refused before anything is launched."""
+    loc, lead, cse = (nat.NativeScheme.of(S.load(n)).handle
+                      for n in ("2x2_locality_ordered", "2x2_locality_lead_single", "2x2_postsum_cse"))
+    m, k = 4096, 17408
+    assert native_lib.lcg_gemm_r7_fused_supported(loc, m, 5120, k) == 1
+    assert native_lib.lcg_gemm_r7_fused_supported(lead, m, 5120, k) == 1
+    assert native_lib.lcg_gemm_r7_fused_supported(cse, m, 5120, k) == 0       # rows of three and four terms
+    assert native_lib.lcg_gemm_r7_fused_supported(loc, m, 5120, 5000) == 0    # K / 2 is not whole K blocks
+    # five two-term planes of (M / 2, K / 2) bf16 behind a 256-byte header
+    assert native_lib.lcg_gemm_r7_ahead_scratch_bytes(loc, m, k) == 256 + 5 * (m // 2) * (k // 2) * 2
+    assert native_lib.lcg_gemm_r7_ahead_scratch_bytes(lead, 257, 256) == 256 + 5 * 129 * 128 * 2
+    assert native_lib.lcg_gemm_r7_ahead_scratch_bytes(cse, m, k) == -1
+    assert native_lib.lcg_gemm_r7_ahead_scratch_bytes(loc, m, 5000) == -1
+    fake = 4096                                   # a non-null, 256-byte aligned address; never dereferenced
+    assert native_lib.lcg_gemm_r7_ahead(loc, fake, k, fake, k // 2, fake, 5120, m, 5120, k, fake, 1024,
+                                        2, 0, None, None) == nat.ERR_BAD_ARG          # scratch too small
+    assert b"scratch" in native_lib.lcg_last_error()
+    assert native_lib.lcg_gemm_r7_ahead(loc, fake, k, fake, k // 2, fake, 5120, m, 5120, k, fake + 8, 1 << 40,
+                                        2, 0, None, None) == nat.ERR_MISALIGNED       # scratch alignment
+    assert native_lib.lcg_gemm_r7_ahead(cse, fake, k, fake, k // 2, fake, 5120, m, 5120, k, fake, 1 << 40,
+                                        2, 0, None, None) == nat.ERR_SCHEME
+    assert native_lib.lcg_gemm_r7_fused(loc, fake, 5000, fake, 2560, fake, 5120, m, 5120, 5000,
+                                        2, 0, None, None) == nat.ERR_UNSUPPORTED_SHAPE

@@ -73,6 +73,21 @@ def test_rank_split_rule():
     assert not down_seam.wants_rank_split((8192, 5120, 37888))      # 16 x 74 tiles: whole waves
 
 
+def test_bare_gemm_dispatch():
+    """Exact-shape dispatch of the bare rank-7 GEMM: narrow outputs form their A planes inside
+    the kernel (rank-split units when whole waves would leave a short last wave), wide ones
+    keep the plane pass and the postsum-CSE decomposition, odd K falls back to planes."""
+    from lcgemm import _native as nat
+    from lcgemm import ops
+
+    assert ops.bare_gemm_form(4096, 5120, 17408) == ("2x2_locality_lead_single", "ahead", nat.SCHEDULE_HYBRID)
+    assert ops.bare_gemm_form(8192, 5120, 17408) == ("2x2_locality_lead_single", "ahead", nat.SCHEDULE_RANK_SPLIT)
+    assert ops.bare_gemm_form(2048, 6144, 16384)[1] == "ahead"
+    assert ops.bare_gemm_form(4096, 34816, 5120) == ("2x2_postsum_cse", "planes", nat.SCHEDULE_HYBRID)
+    assert ops.bare_gemm_form(4096, 13999, 5000) == ("2x2_postsum_cse", "planes", nat.SCHEDULE_HYBRID)
+    assert ops.bare_gemm_form(4096, 5120, 17400)[1] == "planes"            # K % 128 != 0
+
+
 def test_cpu_tensors_are_refused():
     s = S.load("2x2_postsum_cse")
     w = torch.zeros(64, 64, dtype=torch.bfloat16)

@@ -1374,10 +1374,12 @@ extern "C" int lcg_gemm_r7_fused(const lcg_scheme_t* scheme, const void* a, int6
   CUtensorMap ma, mb;
   CMaps mc;
   GemmParams p;
+  FuseParams fuse;
+  if (int e = fill_fuse(scheme, a, lda, M, K, g, &fuse)) return e;      // the scheme, before any driver call
   if (int e = fill_r7(scheme, a, lda, b_planes, ld_b, c, ldc, M, N, g, schedule, cta_group, &ma, &mb,
                       &mc, &p, 0, -1, 0, K))
     return e;
-  if (int e = fill_fuse(scheme, a, lda, M, K, g, &p.fuse)) return e;
+  p.fuse = fuse;
   p.status = status;
   auto st_ = static_cast<cudaStream_t>(stream);
   if (int e = zero_tail_tiles(p, c, ldc, M, N, g, cta_group, st_)) return e;
@@ -1429,11 +1431,8 @@ extern "C" int lcg_gemm_r7_ahead(const lcg_scheme_t* scheme, const void* a, int6
   CUtensorMap ma, mb, ma2;
   CMaps mc;
   GemmParams p;
-  if (int e = fill_r7(scheme, a, lda, b_planes, ld_b, c, ldc, M, N, g, schedule, cta_group, &ma, &mb,
-                      &mc, &p, 0, -1, 0, K))
-    return e;
-  FuseParams& f = p.fuse;
-  if (int e = fill_fuse(scheme, a, lda, M, K, g, &f)) return e;
+  FuseParams f;
+  if (int e = fill_fuse(scheme, a, lda, M, K, g, &f)) return e;         // the scheme, before any driver call
   f.nslots = 0;
   for (int r = 0; r < scheme->rank; ++r) {
     f.slot[r] = -1;
@@ -1450,6 +1449,10 @@ extern "C" int lcg_gemm_r7_ahead(const lcg_scheme_t* scheme, const void* a, int6
   f.scratch = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(scratch) + kAheadHeaderBytes);
   f.chunk_rows = kAheadChunkRows;
   f.chunks = static_cast<int32_t>((g.m2 + kAheadChunkRows - 1) / kAheadChunkRows);
+  if (int e = fill_r7(scheme, a, lda, b_planes, ld_b, c, ldc, M, N, g, schedule, cta_group, &ma, &mb,
+                      &mc, &p, 0, -1, 0, K))
+    return e;
+  p.fuse = f;
   p.status = status;
   auto st_ = static_cast<cudaStream_t>(stream);
   if (f.nslots > 0) {
