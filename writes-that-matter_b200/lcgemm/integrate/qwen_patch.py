@@ -70,18 +70,32 @@ def _(delta, residual, norm_weight, gate_up_weight, down_weight, eps):
 _ATTENTION_TAKES_OUTPUT: dict = {}
 
 
+def _calling_convention(cls):
+    import inspect
+
+    names = inspect.signature(cls.forward).parameters
+    return "output" in names, "positions" in names
+
+
+def _record_attention_conventions(module) -> None:
+    """Fill the table of attention calling conventions from the classes of the model's module,
+    once, at ``arm()``: the patched forward is traced by vLLM's compiler, and traced code must
+    only read this table (a write inside ``forward`` is refused when CUDA graphs are compiled in)."""
+    import inspect
+
+    for name, obj in vars(module).items():
+        if inspect.isclass(obj) and "Attention" in name and callable(getattr(obj, "forward", None)):
+            _ATTENTION_TAKES_OUTPUT[obj] = _calling_convention(obj)
+
+
 def _attention(module, hidden_states, positions=None):
     """Call an attention module under either calling convention vLLM has used for this layer:
     returning its result (the revision the reference pins, ``qwen_patch.py:134-148`` there) or
     filling a caller-allocated ``output`` buffer (the installed 0.22 series)."""
-    cls = type(module)
-    takes_output = _ATTENTION_TAKES_OUTPUT.get(cls)
-    if takes_output is None:
-        import inspect
-
-        names = inspect.signature(module.forward).parameters
-        takes_output = _ATTENTION_TAKES_OUTPUT[cls] = ("output" in names, "positions" in names)
-    wants_output, wants_positions = takes_output
+    convention = _ATTENTION_TAKES_OUTPUT.get(type(module))
+    if convention is None:                         # a class arm() did not see: work it out, store nothing
+        convention = _calling_convention(type(module))
+    wants_output, wants_positions = convention
     kwargs = {"hidden_states": hidden_states}
     if wants_positions and positions is not None:
         kwargs["positions"] = positions
@@ -132,8 +146,10 @@ def arm() -> None:
     if _VLLM_PREIMPORTED and not _CACHE_PRESET:
         raise RuntimeError("qwen_patch must be imported before vLLM unless its compile cache is "
                            "off: a cached stock graph could otherwise be replayed unnoticed")
+    import vllm.model_executor.models.qwen3_5 as qwen3_5
     from vllm.model_executor.models.qwen3_5 import Qwen3_5DecoderLayer
 
+    _record_attention_conventions(qwen3_5)
     if _ORIGINAL_FORWARD is None:
         _ORIGINAL_FORWARD = Qwen3_5DecoderLayer.forward
     Qwen3_5DecoderLayer.forward = _patched_forward
