@@ -59,7 +59,19 @@ def mlp_chain(
     gate_plan, down_plan = plans
     new_residual = _CORE.residual_buffer(delta)
     gate_plan(residual, delta, norm_weight, eps, prepared_w=entry[1], residual_out=new_residual)
-    return down_plan(prepared_w=entry[2]), new_residual
+    out = down_plan(prepared_w=entry[2])
+    # A custom op may not return storage that one of its inputs lives in.  The plans' buffers
+    # are shared by all layers, and a compiled engine is free to hand a layer an input that still
+    # sits in the buffer the previous layer returned (its in-place norms do); the kernels
+    # tolerate that (each reads its inputs before anything overwrites them), the contract does not.
+    inputs = (delta.untyped_storage().data_ptr(), residual.untyped_storage().data_ptr())
+    if out.untyped_storage().data_ptr() in inputs:
+        _CALLS["chain.cloned_output"] += 1
+        out = out.clone()
+    if new_residual.untyped_storage().data_ptr() in inputs:
+        _CALLS["chain.cloned_residual"] += 1
+        new_residual = new_residual.clone()
+    return out, new_residual
 
 
 @mlp_chain.register_fake
