@@ -90,27 +90,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// The same test with a suspend-time hint: a thread whose phase is not complete may stay suspended
-// for up to `hint_ns` (it is woken at once when the phase completes), instead of coming back after
-// the short system-default limit to spin through the loop again.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(hint_ns)
-      : "memory");
-  return ok != 0;
-}
-
-#ifndef LCG_WAIT_HINT_NS
-#define LCG_WAIT_HINT_NS 0
-#endif
-
 // Per-CTA control block for bounded waits.  `abort_flag` lives in shared
 // memory; once any wait of the CTA has run out it is set and every later wait
 // returns at once, so the kernel's control flow (loop trip counts, named
@@ -128,13 +107,8 @@ __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, const
   if (*ctl.abort_flag) return;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
-#if LCG_WAIT_HINT_NS > 0
-  while (!mbar_try_wait_hint(bar, parity, LCG_WAIT_HINT_NS)) {
-    if ((++spins & 0xfu) == 0) {
-#else
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xffu) == 0) {
-#endif
       if (*ctl.abort_flag) return;
       if (globaltimer_ns() - t0 > ctl.limit_ns) {
         *ctl.abort_flag = 1u;
