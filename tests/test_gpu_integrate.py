@@ -84,6 +84,36 @@ def test_qwen_custom_op_dispatch_and_counters(monkeypatch):
     ops.check_status()
 
 
+def test_qwen_custom_op_clones_an_output_that_shares_an_input_buffer(monkeypatch):
+    """A compiled engine may hand layer n + 1 an input that still sits in the plan buffer layer n
+    returned.  The kernels read their inputs before anything overwrites that buffer, so the result
+    must be the one a private copy of the input gives; the op must then return storage of its own
+    (a custom op may not return storage one of its inputs lives in) and count the copy."""
+    from lcgemm import ops
+    from lcgemm.integrate import qwen_patch as qp
+
+    monkeypatch.setattr(qp, "EXPECTED_LAYERS", LAYERS)
+    monkeypatch.setattr(qp, "EXPECTED_SHAPES", (H, I, 2 * I, H))
+    monkeypatch.setitem(qp._STATE, "armed", True)
+    llm = _FakeLLM(qp.LAYER_CLASS_NAME)
+    qp.install(llm, tokens=512)
+    nw = seeded((H,), 5, 0.01)
+    layer = llm.model[0]
+    w_gu, w_d = layer.mlp.gate_up_proj.weight, layer.mlp.down_proj.weight
+    delta, residual = seeded((512, H), 1), seeded((512, H), 2)
+    first, _ = torch.ops.lcgemm_qwen.mlp_chain(delta, residual, nw, w_gu, w_d, 1e-6)
+    shared = first                                   # lives in the plan's output buffer
+    private = first.clone()
+    before = qp.counts().get("chain.cloned_output", 0)
+    want, _ = torch.ops.lcgemm_qwen.mlp_chain(private, residual, nw, w_gu, w_d, 1e-6)
+    want = want.clone()
+    got, _ = torch.ops.lcgemm_qwen.mlp_chain(shared, residual, nw, w_gu, w_d, 1e-6)
+    assert qp.counts().get("chain.cloned_output", 0) == before + 1
+    assert got.untyped_storage().data_ptr() != shared.untyped_storage().data_ptr()
+    assert rel_fro(got, want) <= 8e-3               # rank-split down: bf16 adds in hardware order
+    ops.check_status()
+
+
 def test_muse_two_op_boundary(monkeypatch):
     from lcgemm import ops
     from lcgemm.integrate import muse_patch as mp
