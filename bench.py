@@ -690,8 +690,10 @@ def run_ours(args, rank, world, device):
                     "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": out_host.numel() * 2,
                     "how": "lcgemm.streaming.HostStreamedLayer: each rank copies its tokens/tp rows of "
-                           "the batch from pinned host memory (an all-gather over NVLink replicates "
-                           "them) and its rows of the result back, copies overlapped with compute",
+                           "the batch from pinned host memory, stores them into every peer's input buffer "
+                           "with DMA copies over NVLink on the copy-in stream (a barrier between the ranks "
+                           "on the compute stream follows), and copies its rows of the result back; "
+                           "copies overlapped with compute",
                     "serial_ms_per_step": e2e_serial_ms, "timeline_rank0": timeline},
             "phases_ms": phases,
             "gpu_launches": launches * world,

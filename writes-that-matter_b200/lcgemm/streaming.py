@@ -10,8 +10,14 @@ nothing synchronises the host until :meth:`drain`.
 Under tensor parallelism every rank needs the whole input and, after the exchange, holds the
 whole output.  Copying all of it over every rank's PCIe link would make the host link the
 bottleneck (134 MB per rank and step for 8192 x 8192), so each rank copies only its
-``tokens / tp`` rows in, an all-gather over NVLink replicates them, and each rank copies only
-its own rows of the result out: the batch crosses PCIe once in each direction in total.
+``tokens / tp`` rows in, replicates them over NVLink, and copies only its own rows of the result
+out: the batch crosses PCIe once in each direction in total.  The replication is part of the
+copy-in stage, not of the compute: with ``gather="copy"`` (the default when the ranks share a
+node) every rank's input buffers are symmetric-memory allocations and a rank stores its rows into
+each peer's buffer with one device-to-device copy per peer on the copy-in stream (DMA engines over
+NVLink, no SMs, overlapped with the previous batch's compute); a barrier between the ranks on the
+compute stream (``lcg_peer_barrier``, bounded wait) then says that every rank's rows have landed.
+``gather="nccl"`` keeps the library all-gather on the compute stream.
 """
 from __future__ import annotations
 
@@ -28,7 +34,7 @@ class HostStreamedLayer:
     """
 
     def __init__(self, layer, tokens: int, hidden: int, device=None, group=None, depth: int = 2,
-                 timeline: bool = False):
+                 timeline: bool = False, gather: str = "copy"):
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.layer, self.depth, self.group = layer, depth, group
         self.world = dist.get_world_size(group) if (group is not None or (
@@ -38,7 +44,31 @@ class HostStreamedLayer:
             raise ValueError(f"{tokens} tokens do not split over {self.world} ranks")
         self.rows = tokens // self.world
         bf = torch.bfloat16
-        self.x_dev = [torch.empty((tokens, hidden), device=dev, dtype=bf) for _ in range(depth)]
+        if gather not in ("copy", "nccl"):
+            raise ValueError("gather must be 'copy' or 'nccl'")
+        self.gather = gather if self.world > 1 else None
+        self.peer_rows = None
+        if self.gather == "copy":
+            import os
+
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")     # plain peer copies only
+            import torch.distributed._symmetric_memory as symm
+
+            grp = group if group is not None else dist.group.WORLD
+            self.x_dev = [symm.empty((tokens, hidden), dtype=bf, device=dev) for _ in range(depth)]
+            self._flags = symm.empty((16,), dtype=torch.int32, device=dev)
+            self._flags.zero_()
+            handles = [symm.rendezvous(t, grp) for t in (*self.x_dev, self._flags)]
+            # peer_rows[i][p]: this rank's row slice inside rank p's i-th input buffer
+            off = self.rank * self.rows * hidden
+            self.peer_rows = [[h.get_buffer(p, (self.rows, hidden), bf, off) for p in range(self.world)]
+                              for h in handles[:depth]]
+            self._flag_ptrs = [int(q) for q in handles[depth].buffer_ptrs]
+            self._handles = handles
+            torch.cuda.synchronize(dev)
+            dist.barrier(grp)            # every rank's flags are zero before the first peer barrier
+        else:
+            self.x_dev = [torch.empty((tokens, hidden), device=dev, dtype=bf) for _ in range(depth)]
         self.x_in = ([torch.empty((self.rows, hidden), device=dev, dtype=bf) for _ in range(depth)]
                      if self.world > 1 else self.x_dev)
         self.out_dev = [torch.empty((self.rows, hidden), device=dev, dtype=bf) for _ in range(depth)]
@@ -73,13 +103,22 @@ class HostStreamedLayer:
             if ev:
                 ev["in0"].record()
             self.x_in[i].copy_(x_host, non_blocking=True)
+            if self.gather == "copy":
+                # Safe to overwrite the peers' buffer i: a rank frees it only after its layer call,
+                # whose closing barrier every rank passes after all of them have read their input.
+                for p in range(self.world):
+                    self.peer_rows[i][p].copy_(self.x_in[i], non_blocking=True)
             if ev:
                 ev["in1"].record()
             self.x_ready[i].record()
         compute.wait_event(self.x_ready[i])
         if ev:
             ev["c0"].record(compute)
-        if self.world > 1:
+        if self.gather == "copy":
+            from . import ops
+
+            ops.peer_barrier(self._flag_ptrs, self.rank, 0)       # every rank's rows have landed here
+        elif self.world > 1:
             dist.all_gather_into_tensor(self.x_dev[i], self.x_in[i], group=self.group)
         if ev:
             ev["gathered"].record(compute)
