@@ -126,7 +126,9 @@ int lcg_a_planes(const lcg_scheme_t* scheme, const void* a, int64_t M, int64_t K
  *   h = bf16(float(delta) + float(residual))      -> residual_out (may alias residual)
  *   y = float(h) * rsqrt(mean(h^2) + eps) * (float(norm_weight) + 1)
  *   out plane r = bf16(signed sum of the four blocks of y)
- * delta, residual, residual_out are contiguous (M, K); needs M even, K % 16 == 0. */
+ * delta, residual, residual_out are contiguous (M, K); needs M even, K % 16 == 0.
+ * delta may be NULL (the first layer of a stack, or a layer called on its own): then h is the
+ * residual itself, one operand less is read and residual_out is neither needed nor written. */
 int lcg_norm_planes(const lcg_scheme_t* scheme, const void* delta, const void* residual,
                     const void* norm_weight, int64_t M, int64_t K, float eps,
                     void* residual_out, void* out, int64_t ld_out, void* stream);
@@ -304,7 +306,8 @@ int lcg_static_reserve(void);
 /* ---- dense-arm seams (the stock layer the rank-7 path is compared with) -- */
 
 /* h = bf16(delta + residual) -> residual_out; x = bf16(rmsnorm(h) * (w + 1))
- * (lcgemm/integrate/qwen_patch.py:49-52). Contiguous (M, K), K % 8 == 0. */
+ * (lcgemm/integrate/qwen_patch.py:49-52). Contiguous (M, K), K % 8 == 0.
+ * delta may be NULL as for lcg_norm_planes: h is the residual, residual_out is not written. */
 int lcg_add_rmsnorm(const void* delta, const void* residual, const void* norm_weight,
                     int64_t M, int64_t K, float eps, void* residual_out, void* x,
                     void* stream);

@@ -80,6 +80,15 @@ def test_describe_and_argument_checks_do_not_need_a_gpu(native_lib):
                                         80, None, 0, 0, 0, None, None) == nat.ERR_UNSUPPORTED_SHAPE
     assert native_lib.lcg_norm_planes(sch, fake, fake, fake, 7, 64, 1e-6, fake, fake, 64,
                                       None) == nat.ERR_UNSUPPORTED_SHAPE
+    # a delta needs somewhere to store the sum; without a delta neither is needed (the shape check
+    # comes next, so a missing delta is past the NULL check)
+    assert native_lib.lcg_norm_planes(sch, fake, fake, fake, 8, 64, 1e-6, None, fake, 64,
+                                      None) == nat.ERR_BAD_ARG
+    assert native_lib.lcg_norm_planes(sch, None, fake, fake, 7, 64, 1e-6, None, fake, 64,
+                                      None) == nat.ERR_UNSUPPORTED_SHAPE
+    assert native_lib.lcg_add_rmsnorm(fake, fake, fake, 8, 64, 1e-6, None, fake, None) == nat.ERR_BAD_ARG
+    assert native_lib.lcg_add_rmsnorm(None, fake, fake, 8, 60, 1e-6, None, fake,
+                                      None) == nat.ERR_UNSUPPORTED_SHAPE
     assert native_lib.lcg_gemm_r7(sch, fake, 64, fake, 64, fake, 64, 64, 64, 128, 5, 0, None,
                                   None) == nat.ERR_BAD_ARG
     assert native_lib.lcg_launch_count() == 0

@@ -125,6 +125,26 @@ def test_layer_arms_small_against_reference(lc):
         assert torch.equal(out.cpu().view(torch.int16), want.view(torch.int16))
 
 
+def test_layer_without_a_delta_is_the_layer_with_a_zero_delta(lc):
+    """`layer(x)` runs the single-input norm kernels; at this size every arm is bit-reproducible
+    (all-ranks schedules), so the outputs must be the bits of `layer(x, zeros)`."""
+    m, h, i = 256, 256, 512
+    _, x, nw, wgu, wd = _layer_inputs(m, h, i, seed=21)
+    zero = torch.zeros_like(x)
+    for arm in (lc.layer.Rank7MlpLayer(m, nw, wgu, wd), lc.layer.DenseMlpLayer(m, nw, wgu, wd)):
+        if isinstance(arm, lc.layer.Rank7MlpLayer):
+            from lcgemm._native import SCHEDULE_ALL_RANKS
+
+            arm.gate_plan.schedule = SCHEDULE_ALL_RANKS
+            arm.down_plan.rank_split = False
+        want = arm(x, zero).clone()
+        d, hh = arm.chain(None, x)
+        assert hh is x
+        got = arm(x)
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    lc.ops.check_status()
+
+
 def test_plan_shape_errors(lc):
     gs, ds = lc.load(GATE), lc.load(DOWN)
     with pytest.raises(ValueError):

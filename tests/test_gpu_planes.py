@@ -57,6 +57,40 @@ def test_norm_planes(lc, shape):
     assert mismatch_fraction(out, want) < 2e-3
 
 
+@pytest.mark.parametrize("name", NAMES + ("2x2_locality_lead_single",))
+@pytest.mark.parametrize("shape", [(64, 256), (130, 5120), (36, 7168), (32, 8192), (12, 9216), (8, 16400)])
+def test_norm_planes_without_delta(lc, name, shape):
+    """No delta: the residual stream is the input itself.  Every kernel form (register, lean, staged,
+    generic; compile-time and run-time tables) must give the bits it gives for a delta of zeros, and
+    must leave the residual_out argument alone."""
+    m, k = shape
+    sch = lc.load(name)
+    residual, nw = seeded(shape, 4), seeded((k,), 5, 0.01)
+    zero = torch.zeros_like(residual)
+    want = torch.empty(lc.ops.a_plane_shape(sch, m, k), device="cuda", dtype=torch.bfloat16)
+    lc.ops.norm_planes(sch, zero, residual, nw, 1e-6, torch.empty_like(residual), want)
+    got = torch.full_like(want, float("nan"))
+    lc.ops.norm_planes(sch, None, residual, nw, 1e-6, None, got)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    lc.ops.check_status()
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_norm_planes_lean_form_matches_the_other_forms(lc, name):
+    """K = 6656 is the widest row the 416-thread register kernel takes, K = 6672 the narrowest the
+    lean one takes with a delta, K = 8192 its widest: each against the oracle."""
+    tb, sch = O.Tables(name), lc.load(name)
+    for m, k in ((20, 6656), (20, 6672), (20, 8192)):
+        delta, residual, nw = seeded((m, k), 3), seeded((m, k), 4), seeded((k,), 5, 0.01)
+        out = torch.empty(lc.ops.a_plane_shape(sch, m, k), device="cuda", dtype=torch.bfloat16)
+        res_out = torch.empty_like(delta)
+        lc.ops.norm_planes(sch, delta, residual, nw, 1e-6, res_out, out)
+        want, h = O.norm_planes(delta.cpu(), residual.cpu(), nw.cpu(), 1e-6, tb)
+        assert torch.equal(res_out.cpu().view(torch.int16), h.view(torch.int16))
+        assert within_ulps(out, want, 1.0, floor=2e-3)
+        assert mismatch_fraction(out, want) < 2e-3
+
+
 def test_norm_planes_in_place_residual(lc):
     sch = lc.load("2x2_postsum_cse")
     delta, residual = seeded((64, 512), 8), seeded((64, 512), 9)
@@ -89,8 +123,9 @@ def test_prepare_down_b_matches_oracle(lc):
     assert torch.equal(got.cpu().view(torch.int16), O.prepare_down_b(w.cpu(), tb).view(torch.int16))
 
 
-def test_dense_arm_seams(lc):
-    m, k = 96, 5120
+@pytest.mark.parametrize("m,k", [(96, 5120), (95, 5120), (64, 8192), (16, 8200)])
+def test_dense_arm_seams(lc, m, k):
+    """Even row counts up to K = 8192 take the register kernel, the rest the staged one."""
     delta, residual, nw = seeded((m, k), 1), seeded((m, k), 2), seeded((k,), 3, 0.01)
     x, h = lc.ops.add_rmsnorm(delta, residual, nw, 1e-6)
     hc = (delta.cpu().float() + residual.cpu().float()).to(torch.bfloat16)
@@ -100,6 +135,10 @@ def test_dense_arm_seams(lc):
     assert within_ulps(x, want, 1.0, floor=1e-3) and mismatch_fraction(x, want) < 2e-3
     y = lc.ops.add(delta, residual)
     assert torch.equal(y.cpu(), hc)
+    # without a delta: the bits of a zero delta, and the residual handed back as the stream
+    x0, _ = lc.ops.add_rmsnorm(torch.zeros_like(residual), residual, nw, 1e-6)
+    x1, h1 = lc.ops.add_rmsnorm(None, residual, nw, 1e-6)
+    assert torch.equal(x0, x1) and h1 is residual
 
 
 def test_shape_and_device_errors(lc):

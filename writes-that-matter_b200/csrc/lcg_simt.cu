@@ -162,15 +162,19 @@ k_norm_planes(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __re
       for (int kb = 0; kb < 2; ++kb) {
         if (v < nvec) {
           const int64_t off = (i * m2 + rho) * k + kb * k2 + v * 8;
-          float d[8], r[8], s[8];
-          unpack8(*reinterpret_cast<const Vec8*>(delta + off), d);
-          unpack8(*reinterpret_cast<const Vec8*>(residual + off), r);
+          if (delta != nullptr) {
+            float d[8], r[8], s[8];
+            unpack8(*reinterpret_cast<const Vec8*>(delta + off), d);
+            unpack8(*reinterpret_cast<const Vec8*>(residual + off), r);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) s[e] = d[e] + r[e];
-          // The norm must see exactly the value that is stored as the new
-          // residual stream, so round first.
-          h[t][i][kb] = pack8(s);
-          *reinterpret_cast<Vec8*>(residual_out + off) = h[t][i][kb];
+            for (int e = 0; e < 8; ++e) s[e] = d[e] + r[e];
+            // The norm must see exactly the value that is stored as the new
+            // residual stream, so round first.
+            h[t][i][kb] = pack8(s);
+          } else {
+            h[t][i][kb] = *reinterpret_cast<const Vec8*>(residual + off);   // no delta: h is the residual
+          }
+          if (residual_out != nullptr) *reinterpret_cast<Vec8*>(residual_out + off) = h[t][i][kb];
           float hf[8];
           unpack8(h[t][i][kb], hf);
 #pragma unroll
@@ -257,7 +261,7 @@ k_norm_planes_staged(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat1
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb) {
         const size_t off = (static_cast<size_t>(i) * m2 + rho) * k + kb * k2 + v * 8;
-        cp_async16(&stage[((i * 2 + kb) * 2 + 0) * nvec + v], delta + off);
+        if (delta != nullptr) cp_async16(&stage[((i * 2 + kb) * 2 + 0) * nvec + v], delta + off);
         cp_async16(&stage[((i * 2 + kb) * 2 + 1) * nvec + v], residual + off);
       }
   asm volatile("cp.async.commit_group;" ::: "memory");
@@ -269,14 +273,17 @@ k_norm_planes_staged(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat1
     for (int i = 0; i < 2; ++i)
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb) {
-        float d[8], r[8], s[8];
-        unpack8(stage[((i * 2 + kb) * 2 + 0) * nvec + v], d);
-        unpack8(stage[((i * 2 + kb) * 2 + 1) * nvec + v], r);
+        Vec8 h = stage[((i * 2 + kb) * 2 + 1) * nvec + v];      // no delta: h is the residual
+        if (delta != nullptr) {
+          float d[8], r[8], s[8];
+          unpack8(stage[((i * 2 + kb) * 2 + 0) * nvec + v], d);
+          unpack8(h, r);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) s[e] = d[e] + r[e];
-        const Vec8 h = pack8(s);          // the norm sees exactly what is stored as the residual
+          for (int e = 0; e < 8; ++e) s[e] = d[e] + r[e];
+          h = pack8(s);                   // the norm sees exactly what is stored as the residual
+        }
         const size_t off = (static_cast<size_t>(i) * m2 + rho) * k + kb * k2 + v * 8;
-        *reinterpret_cast<Vec8*>(residual_out + off) = h;
+        if (residual_out != nullptr) *reinterpret_cast<Vec8*>(residual_out + off) = h;
         stage[((i * 2 + kb) * 2 + 0) * nvec + v] = h;
         float hf[8];
         unpack8(h, hf);
@@ -433,6 +440,113 @@ k_norm_planes_reg(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* 
   }
 }
 
+// The register form at 64 registers, for rows of up to 512 vectors per block column (K <= 8192)
+// and for a call without a delta.  Two 512-thread CTAs fit an SM because nothing but h (packed
+// bf16) lives across the barrier: each plane recomputes its normalised terms from h, the row's
+// 1 / rms and the weight vector -- the same multiplications in the same order as the other forms,
+// so the same bits.  kHasDelta false: h is the residual itself, no sum is formed and nothing is
+// stored for the residual stream (four loads and seven stores per thread instead of eight and
+// eleven).
+template <unsigned long long kCode, bool kHasDelta>
+__global__ void __launch_bounds__(512, 2)
+k_norm_planes_lean(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __restrict__ residual,
+                   const __nv_bfloat16* __restrict__ norm_w, int m2, int k, float eps,
+                   __nv_bfloat16* residual_out, __nv_bfloat16* __restrict__ out, int ld_out) {
+  __shared__ float s_part[2][16];
+  const int rho = blockIdx.x;
+  const int k2 = k / 2;
+  const int nvec = k2 / 8;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const bool live = tid < nvec;
+  const int v = live ? tid : 0;
+
+  Vec8 h[2][2];
+  if constexpr (kHasDelta) {
+    Vec8 d[2][2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) {
+        const size_t off = (static_cast<size_t>(i) * m2 + rho) * k + kb * k2 + v * 8;
+        d[i][kb] = ldg_stream(delta + off);
+        h[i][kb] = ldg_stream(residual + off);
+      }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) {
+        float df[8], rf[8], sf[8];
+        unpack8(d[i][kb], df);
+        unpack8(h[i][kb], rf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sf[e] = df[e] + rf[e];
+        h[i][kb] = pack8(sf);             // the norm sees exactly what is stored as the residual
+        if (live && residual_out != nullptr)
+          stg_stream(residual_out + (static_cast<size_t>(i) * m2 + rho) * k + kb * k2 + v * 8, h[i][kb]);
+      }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb)
+        h[i][kb] = ldg_stream(residual + (static_cast<size_t>(i) * m2 + rho) * k + kb * k2 + v * 8);
+  }
+  float ss[2] = {0.f, 0.f};
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) {
+        float hf[8];
+        unpack8(h[i][kb], hf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss[i] = fmaf(hf[e], hf[e], ss[i]);
+      }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], o);
+    if (lane == 0) s_part[i][warp] = ss[i];
+  }
+  __syncthreads();
+  float rstd[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float part = lane < nwarps ? s_part[i][lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    rstd[i] = rsqrtf(part / static_cast<float>(k) + eps);
+  }
+  if (!live) return;
+  Vec8 wv[2];
+#pragma unroll
+  for (int kb = 0; kb < 2; ++kb) wv[kb] = *reinterpret_cast<const Vec8*>(norm_w + kb * k2 + v * 8);
+  __nv_bfloat16* dst = out + static_cast<size_t>(rho) * ld_out + v * 8;
+  const size_t plane_stride = static_cast<size_t>(m2) * ld_out;
+#pragma unroll
+  for (int rr = 0; rr < kMaxRank; ++rr) {
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = 0.f;          // from +0, block order, as signed_sum_fixed
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const int c = code_coef(kCode, rr, x);
+      if (c != 1 && c != 3) continue;
+      float hf[8], wf[8];
+      unpack8(h[x >> 1][x & 1], hf);
+      unpack8(wv[x & 1], wf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float y = __fmul_rn(__fmul_rn(hf[e], rstd[x >> 1]), __fadd_rn(wf[e], 1.0f));
+        o[e] = c == 1 ? __fadd_rn(o[e], y) : __fsub_rn(o[e], y);
+      }
+    }
+    stg_stream(dst + rr * plane_stride, pack8(o));
+  }
+}
+
 // --------------------------------------------------------- SwiGLU + planes
 __device__ __forceinline__ float silu_f32(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
@@ -480,13 +594,16 @@ k_add_rmsnorm(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __re
   float ss = 0.f;
   for (int64_t v = tid; v < nvec; v += blockDim.x) {
     const int64_t off = row * k + v * 8;
-    float d[8], r[8], s[8];
-    unpack8(*reinterpret_cast<const Vec8*>(delta + off), d);
-    unpack8(*reinterpret_cast<const Vec8*>(residual + off), r);
+    Vec8 hv = *reinterpret_cast<const Vec8*>(residual + off);      // no delta: h is the residual
+    if (delta != nullptr) {
+      float d[8], r[8], s[8];
+      unpack8(*reinterpret_cast<const Vec8*>(delta + off), d);
+      unpack8(hv, r);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) s[e] = d[e] + r[e];
-    const Vec8 hv = pack8(s);
-    *reinterpret_cast<Vec8*>(residual_out + off) = hv;
+      for (int e = 0; e < 8; ++e) s[e] = d[e] + r[e];
+      hv = pack8(s);
+    }
+    if (residual_out != nullptr) *reinterpret_cast<Vec8*>(residual_out + off) = hv;
     s_row[v] = hv;
     float hf[8];
     unpack8(hv, hf);
@@ -508,6 +625,77 @@ k_add_rmsnorm(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __re
 #pragma unroll
     for (int e = 0; e < 8; ++e) y[e] = hf[e] * rstd * (w[e] + 1.0f);
     *reinterpret_cast<Vec8*>(x + row * k + v * 8) = pack8(y);
+  }
+}
+
+// The same seam for rows of at most 1024 vectors (K <= 8192) and an even row count, in the style
+// of the rank-7 arm's register kernel so that the two arms' norm kernels run at the same fraction
+// of HBM: one CTA per pair of adjacent rows, one thread per vector of both rows, every load issued
+// before anything is consumed, h kept packed in registers, streaming loads and stores.
+__global__ void __launch_bounds__(1024)
+k_add_rmsnorm_reg(const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __restrict__ residual,
+                  const __nv_bfloat16* __restrict__ norm_w, int k, float eps,
+                  __nv_bfloat16* residual_out, __nv_bfloat16* __restrict__ x) {
+  __shared__ float s_part[2][32];
+  const int nvec = k / 8;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const bool live = tid < nvec;
+  const int v = live ? tid : 0;
+  const size_t base = static_cast<size_t>(blockIdx.x) * 2 * k + v * 8;
+  Vec8 h[2];
+  if (delta != nullptr) {
+    Vec8 d[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      d[i] = ldg_stream(delta + base + static_cast<size_t>(i) * k);
+      h[i] = ldg_stream(residual + base + static_cast<size_t>(i) * k);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float df[8], rf[8], sf[8];
+      unpack8(d[i], df);
+      unpack8(h[i], rf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sf[e] = df[e] + rf[e];
+      h[i] = pack8(sf);
+      if (live && residual_out != nullptr) stg_stream(residual_out + base + static_cast<size_t>(i) * k, h[i]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) h[i] = ldg_stream(residual + base + static_cast<size_t>(i) * k);
+  }
+  float ss[2] = {0.f, 0.f};
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float hf[8];
+      unpack8(h[i], hf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss[i] = fmaf(hf[e], hf[e], ss[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], o);
+    if (lane == 0) s_part[i][warp] = ss[i];
+  }
+  __syncthreads();
+  if (!live) return;
+  float w[8];
+  unpack8(*reinterpret_cast<const Vec8*>(norm_w + v * 8), w);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float part = lane < nwarps ? s_part[i][lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    const float rstd = rsqrtf(part / static_cast<float>(k) + eps);
+    float hf[8], y[8];
+    unpack8(h[i], hf);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = hf[e] * rstd * (w[e] + 1.0f);
+    stg_stream(x + base + static_cast<size_t>(i) * k, pack8(y));
   }
 }
 
@@ -602,28 +790,35 @@ extern "C" int lcg_a_planes(const lcg_scheme_t* scheme, const void* a, int64_t M
 extern "C" int lcg_norm_planes(const lcg_scheme_t* scheme, const void* delta, const void* residual,
                                const void* norm_weight, int64_t M, int64_t K, float eps,
                                void* residual_out, void* out, int64_t ld_out, void* stream) {
-  if (!scheme || !delta || !residual || !norm_weight || !residual_out || !out)
+  if (!scheme || !residual || !norm_weight || !out || (delta && !residual_out))
     return fail(LCG_ERR_BAD_ARG, "NULL argument");
+  if (!delta) residual_out = nullptr;       // no delta: the residual stream is the input, nothing is stored
   if (M < 2 || M % 2 != 0 || K < 16 || K % 16 != 0)
     return fail(LCG_ERR_UNSUPPORTED_SHAPE,
                 "fused norm needs an even M and K %% 16 == 0, got M=%lld K=%lld", (long long)M,
                 (long long)K);
-  if (!aligned16(delta) || !aligned16(residual) || !aligned16(norm_weight) ||
-      !aligned16(residual_out) || !aligned16(out))
+  if ((delta && !aligned16(delta)) || !aligned16(residual) || !aligned16(norm_weight) ||
+      (residual_out && !aligned16(residual_out)) || !aligned16(out))
     return fail(LCG_ERR_MISALIGNED, "all operands must be 16-byte aligned");
   const int64_t k2p = (K / 2 + 63) / 64 * 64;
   if (ld_out < k2p || ld_out % 8 != 0)
     return fail(LCG_ERR_BAD_ARG, "plane leading dimension %lld must be >= %lld and a multiple of 8",
                 (long long)ld_out, (long long)k2p);
   const int64_t nvec_p = k2p / 8;
-  // Register form: a shipped table and rows of at most 416 vectors per block column.
-  if (k2p == K / 2 && K / 16 <= 416 && M / 2 <= 0x7fffffff && ld_out <= 0x7fffffff) {
+  // Register forms: a shipped table and rows of at most 512 vectors per block column.  The lean
+  // one takes the rows too wide for the other and every call without a delta.
+  if (k2p == K / 2 && K / 16 <= 512 && M / 2 <= 0x7fffffff && ld_out <= 0x7fffffff) {
     const TermTable table = a_table(scheme);
     const unsigned long long code = table_code(table, scheme->rank);
     if (code == kCodePostsumA || code == kCodeLocalityA) {
       const int nvec = static_cast<int>(K / 16);
       const int threads = (nvec + 31) / 32 * 32;
-      auto kern = code == kCodePostsumA ? k_norm_planes_reg<kCodePostsumA> : k_norm_planes_reg<kCodeLocalityA>;
+      const bool postsum = code == kCodePostsumA;
+      auto kern = postsum ? k_norm_planes_reg<kCodePostsumA> : k_norm_planes_reg<kCodeLocalityA>;
+      if (!delta)
+        kern = postsum ? k_norm_planes_lean<kCodePostsumA, false> : k_norm_planes_lean<kCodeLocalityA, false>;
+      else if (nvec > 416)
+        kern = postsum ? k_norm_planes_lean<kCodePostsumA, true> : k_norm_planes_lean<kCodeLocalityA, true>;
       kern<<<static_cast<unsigned>(M / 2), threads, 0, static_cast<cudaStream_t>(stream)>>>(
           static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(residual),
           static_cast<const __nv_bfloat16*>(norm_weight), static_cast<int>(M / 2), static_cast<int>(K), eps,
@@ -710,15 +905,25 @@ extern "C" int lcg_swiglu_planes(const lcg_scheme_t* plane_scheme, const void* z
 extern "C" int lcg_add_rmsnorm(const void* delta, const void* residual, const void* norm_weight,
                                int64_t M, int64_t K, float eps, void* residual_out, void* x,
                                void* stream) {
-  if (!delta || !residual || !norm_weight || !residual_out || !x)
+  if (!residual || !norm_weight || !x || (delta && !residual_out))
     return fail(LCG_ERR_BAD_ARG, "NULL argument");
+  if (!delta) residual_out = nullptr;       // no delta: the residual stream is the input, nothing is stored
   if (M < 1 || K < 8 || K % 8 != 0 || K > 24576)
     return fail(LCG_ERR_UNSUPPORTED_SHAPE, "needs K %% 8 == 0 and K <= 24576, got K=%lld", (long long)K);
-  if (!aligned16(delta) || !aligned16(residual) || !aligned16(norm_weight) ||
-      !aligned16(residual_out) || !aligned16(x))
+  if ((delta && !aligned16(delta)) || !aligned16(residual) || !aligned16(norm_weight) ||
+      (residual_out && !aligned16(residual_out)) || !aligned16(x))
     return fail(LCG_ERR_MISALIGNED, "all operands must be 16-byte aligned");
   const int64_t nvec = K / 8;
   const int threads = static_cast<int>(nvec >= 1024 ? 1024 : (nvec + 31) / 32 * 32);
+  if (nvec <= 1024 && M % 2 == 0 && M / 2 <= 0x7fffffff) {
+    k_add_rmsnorm_reg<<<static_cast<unsigned>(M / 2), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(residual),
+        static_cast<const __nv_bfloat16*>(norm_weight), static_cast<int>(K), eps,
+        static_cast<__nv_bfloat16*>(residual_out), static_cast<__nv_bfloat16*>(x));
+    LCG_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return LCG_OK;
+  }
   k_add_rmsnorm<<<static_cast<unsigned>(M), threads, static_cast<size_t>(K) * 2,
                   static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(residual),

@@ -33,24 +33,23 @@ class Rank7MlpLayer:
         self.gate_bw = self.gate_plan.prepare_weight(gate_up_weight)
         self.down_bw = self.down_plan.prepare_weight(down_weight)
         self.out = torch.empty((tokens, out_dim), device=gate_up_weight.device, dtype=torch.bfloat16)
-        self._zero = None
 
     def chain(self, delta, residual):
-        """``(down_out, residual_out)`` exactly as the custom op returns them."""
+        """``(down_out, residual_out)`` exactly as the custom op returns them.  Without a ``delta``
+        (``None``: the layer on its own, as in the single-layer configuration) the residual stream is
+        ``residual`` itself and the norm kernel reads one operand and stores no sum."""
         self.gate_plan(residual, delta, self.norm_weight, self.eps, prepared_w=self.gate_bw)
-        return self.down_plan(prepared_w=self.down_bw), self.gate_plan.residual_out
+        h = residual if delta is None else self.gate_plan.residual_out
+        return self.down_plan(prepared_w=self.down_bw), h
 
     def forward(self, x, delta=None):
-        """``h + mlp(norm(h))`` with ``h = x + delta`` (``delta`` defaults to zero)."""
-        if delta is None:
-            if self._zero is None or self._zero.shape != x.shape:
-                self._zero = torch.zeros_like(x)
-            delta = self._zero
+        """``h + mlp(norm(h))`` with ``h = x + delta`` (``h = x`` without a ``delta``)."""
         down_out, h = self.chain(delta, x)
         return ops.add(h, down_out if down_out.is_contiguous() else down_out.contiguous(), out=self.out)
 
     __call__ = forward
     launches_per_forward = 4
+    accepts_no_delta = True
 
 
 class DenseMlpLayer:
@@ -69,7 +68,6 @@ class DenseMlpLayer:
         self.s = torch.empty((tokens, inter), device=dev, dtype=bf)
         self.d = torch.empty((tokens, out_dim), device=dev, dtype=bf)
         self.out = torch.empty((tokens, out_dim), device=dev, dtype=bf)
-        self._zero = None
 
     def _mm(self, a, w, out):
         if self.gemm == "cublas":
@@ -77,22 +75,19 @@ class DenseMlpLayer:
         return ops.gemm_dense(a, w, out=out, cta_group=self.cta_group)
 
     def chain(self, delta, residual):
-        ops.add_rmsnorm(delta, residual, self.norm_weight, self.eps, residual_out=self.h, x=self.x)
+        _, h = ops.add_rmsnorm(delta, residual, self.norm_weight, self.eps, residual_out=self.h, x=self.x)
         self._mm(self.x, self.w_gu, self.z)
         ops.swiglu(self.z, out=self.s)
         self._mm(self.s, self.w_down, self.d)
-        return self.d, self.h
+        return self.d, h                      # without a delta h is `residual` itself
 
     def forward(self, x, delta=None):
-        if delta is None:
-            if self._zero is None or self._zero.shape != x.shape:
-                self._zero = torch.zeros_like(x)
-            delta = self._zero
         d, h = self.chain(delta, x)
         return ops.add(h, d, out=self.out)
 
     __call__ = forward
     launches_per_forward = 5
+    accepts_no_delta = True
 
 
 class CapturedLayer:

@@ -99,19 +99,27 @@ def a_planes(a: torch.Tensor, scheme, out: torch.Tensor | None = None) -> torch.
 
 
 def norm_planes(scheme, delta, residual, norm_weight, eps: float, residual_out, out) -> None:
-    for t, what in ((delta, "delta"), (residual, "residual"), (norm_weight, "norm weight"),
-                    (residual_out, "residual_out"), (out, "A planes")):
+    """A planes of ``norm(delta + residual)`` into ``out``, the sum into ``residual_out``.  Without a
+    ``delta`` (``None``) the sum is ``residual`` itself: ``residual_out`` is ignored."""
+    tensors = [(residual, "residual"), (norm_weight, "norm weight"), (out, "A planes")]
+    shaped = [(residual, "residual")]
+    if delta is not None:
+        tensors += [(delta, "delta"), (residual_out, "residual_out")]
+        shaped += [(delta, "delta"), (residual_out, "residual_out")]
+    for t, what in tensors:
         _need(t, what)
-    m, k = delta.shape
-    for t, what in ((delta, "delta"), (residual, "residual"), (residual_out, "residual_out")):
+    m, k = residual.shape
+    for t, what in shaped:
         if tuple(t.shape) != (m, k) or not t.is_contiguous():
             raise ValueError(f"{what} must be a contiguous ({m}, {k}) tensor")
     if tuple(norm_weight.shape) != (k,):
         raise ValueError(f"norm weight must be ({k},)")
     if tuple(out.shape) != a_plane_shape(scheme, m, k):
         raise ValueError(f"A workspace must be {a_plane_shape(scheme, m, k)}, got {tuple(out.shape)}")
-    check(lib().lcg_norm_planes(NativeScheme.of(scheme).handle, ptr(delta), ptr(residual),
-                                ptr(norm_weight), m, k, float(eps), ptr(residual_out), ptr(out),
+    check(lib().lcg_norm_planes(NativeScheme.of(scheme).handle,
+                                None if delta is None else ptr(delta), ptr(residual),
+                                ptr(norm_weight), m, k, float(eps),
+                                None if delta is None else ptr(residual_out), ptr(out),
                                 out.stride(0), stream_ptr()))
 
 
@@ -385,13 +393,23 @@ def reduce_gather(slots: torch.Tensor, h: torch.Tensor, out_ptrs, rows_per_owner
 
 # -------------------------------------------------------------- dense seams
 def add_rmsnorm(delta, residual, norm_weight, eps: float, residual_out=None, x=None):
-    for t, what in ((delta, "delta"), (residual, "residual"), (norm_weight, "norm weight")):
+    """``(norm(delta + residual), delta + residual)``; without a ``delta`` the second value is
+    ``residual`` itself and nothing is stored for it."""
+    for t, what in ((residual, "residual"), (norm_weight, "norm weight")):
         _need(t, what)
-    m, k = delta.shape
+    m, k = residual.shape
+    if x is None:
+        x = torch.empty_like(residual)
+    if delta is None:
+        for t in (residual, x):
+            if tuple(t.shape) != (m, k) or not t.is_contiguous():
+                raise ValueError(f"operands must be contiguous ({m}, {k}) tensors")
+        check(lib().lcg_add_rmsnorm(None, ptr(residual), ptr(norm_weight), m, k, float(eps),
+                                    None, ptr(x), stream_ptr()))
+        return x, residual
+    _need(delta, "delta")
     if residual_out is None:
         residual_out = torch.empty_like(delta)
-    if x is None:
-        x = torch.empty_like(delta)
     for t in (delta, residual, residual_out, x):
         if tuple(t.shape) != (m, k) or not t.is_contiguous():
             raise ValueError(f"operands must be contiguous ({m}, {k}) tensors")

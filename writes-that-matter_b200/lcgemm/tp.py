@@ -150,7 +150,7 @@ class TensorParallelMlp:
             gate.preclear = gate.c                   # nothing to clear: the push GEMM initialises its output
 
     def forward(self, x: torch.Tensor, delta: torch.Tensor | None = None) -> torch.Tensor:
-        if delta is None:
+        if delta is None and not getattr(self.layer, "accepts_no_delta", False):
             if self._zero is None or self._zero.shape != x.shape:
                 self._zero = torch.zeros_like(x)
             delta = self._zero
@@ -188,7 +188,8 @@ class TensorParallelMlp:
         ops.gemm_r7_push(down.scheme, down.a_planes(), lay.down_bw, m, n, k, down.c, ex.slot_ptrs[b],
                          ex.rank, ex.rows, cta_group=down.cta_group)
         ex.barrier()                 # every rank's pushes have landed
-        ops.reduce_gather(ex.slots[b], gate.residual_out, ex.out_ptrs, ex.rows, ex.rank)
+        h = x if delta is None else gate.residual_out      # without a delta the residual stream is x
+        ops.reduce_gather(ex.slots[b], h, ex.out_ptrs, ex.rows, ex.rank)
         ex.barrier()                 # every owner's rows have landed here
         self.out = ex.out
         return self.out
@@ -199,7 +200,7 @@ class TensorParallelMlp:
         lay = self.layer
         gate, down = lay.gate_plan, lay.down_plan
         gate(x, delta, lay.norm_weight, lay.eps, prepared_w=lay.gate_bw)   # also zeroes down.c
-        h = gate.residual_out
+        h = x if delta is None else gate.residual_out
         if down.rank_split and gate.preclear is not down.c:
             down.c.zero_()
         total = down.tile_rows
