@@ -939,7 +939,10 @@ def run_case(args, device):
     x, nw, wgu, wd = make_layer_tensors(m, h, i, device)
     gate, down = build_chain((m, h, 2 * i), (m, i, h))
     zero = torch.zeros_like(x)
-    if args.case in ("gate_up", "norm_planes", "down"):
+    if args.case == "norm_planes_single":
+        # the norm + A-plane kernel as the single-layer call runs it: no delta, no residual stream
+        fn, flops = (lambda: gate.a_planes(x, None, nw, EPS)), 0.0
+    elif args.case in ("gate_up", "norm_planes", "down"):
         gate_bw = gate.prepare_weight(wgu)
         a = gate.a_planes(x, zero, nw, EPS)
         gate.gemm(a, gate_bw)
@@ -1313,7 +1316,7 @@ def main():
     ap.add_argument("--prompts", type=int, default=8, help="seeded prompts per length for --model's agreement rates")
     ap.add_argument("--model-tokens", default="2048,4096,8192", help="prompt lengths for --model")
     ap.add_argument("--case", default=None,
-                    help="time one kernel alone: gate_up | down | norm_planes | a_planes | bare_ahead | dense_gate_up; "
+                    help="time one kernel alone: gate_up | down | norm_planes | norm_planes_single | a_planes | bare_ahead | dense_gate_up; "
                          "or `layer`: the whole layer's three arms at --tokens / --hidden / --inter")
     ap.add_argument("--tokens", type=int, default=4096, help="token count for --case")
     ap.add_argument("--hidden", type=int, default=SINGLE["hidden"], help="hidden size for --case")
