@@ -29,6 +29,20 @@ class _CpuLayer:
         return O.mlp_reference(delta, residual, nw, wgu, wd, eps)
 
 
+class _CpuLayerSingleInput(_CpuLayer):
+    """A layer that takes a call without a delta itself (as the CUDA layers do): the residual
+    stream it hands back is then its input."""
+
+    accepts_no_delta = True
+
+    def chain(self, delta, residual):
+        self.saw_delta = delta is not None
+        if delta is None:
+            out, _ = super().chain(torch.zeros_like(residual), residual)
+            return out, residual
+        return super().chain(delta, residual)
+
+
 def _worker(rank, world, port, ret):
     import sys
     from pathlib import Path
@@ -60,6 +74,13 @@ def _worker(rank, world, port, ret):
         want = add(href, full)
         err = ((out.float() - want.float()).norm() / want.float().norm()).item()
         mlp_err = ((seen["reduced"].float() - full.float()).norm() / full.float().norm()).item()
+        # a layer that says it takes a missing delta gets None, not a zeros tensor; same result
+        single = tp.TensorParallelMlp(m, nw, gu_shard, d_shard, 1e-6, make_layer=_CpuLayerSingleInput, add=add)
+        out1 = single(x)
+        assert single.layer.saw_delta is False and torch.equal(out1, out)
+        single(x, torch.zeros_like(x))
+        assert single.layer.saw_delta is True
+        assert layer._zero is not None and single._zero is None
         ret[rank] = (err, mlp_err)
     finally:
         dist.destroy_process_group()
