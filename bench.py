@@ -443,12 +443,11 @@ def bench_layer_arms(tokens, hidden, inter, steps, warmup, flush, device, with_p
     r7 = Rank7MlpLayer(tokens, nw, wgu, wd, EPS)
     dn = DenseMlpLayer(tokens, nw, wgu, wd, EPS, gemm="tcgen05")
     cb = DenseMlpLayer(tokens, nw, wgu, wd, EPS, gemm="cublas")
-    zero = torch.zeros_like(x)
     part_events = []
 
-    def r7_step():
+    def r7_step():                      # r7(x) kernel by kernel, so that events can sit around the gate_up GEMM
         gp, dp = r7.gate_plan, r7.down_plan
-        a = gp.a_planes(x, zero, nw, EPS)
+        a = gp.a_planes(x, None, nw, EPS)
         if with_parts and collecting[0]:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -458,7 +457,7 @@ def bench_layer_arms(tokens, hidden, inter, steps, warmup, flush, device, with_p
         else:
             gp.gemm(a, r7.gate_bw)
         d = dp(prepared_w=r7.down_bw)
-        ops.add(gp.residual_out, d, out=r7.out)
+        ops.add(x, d, out=r7.out)
 
     collecting = [False]
     arms = {"rank7": r7_step, "dense_tcgen05": lambda: dn(x), "dense_cublas": lambda: cb(x)}
@@ -575,6 +574,8 @@ def run_ours(args, rank, world, device):
         sub_steps = max(5, args.steps // 2)
         gemm_only = gemm_only_block(cfg["tokens"], cfg["hidden"], cfg["inter"], sub_steps, args.warmup, flush, device)
         torch.cuda.empty_cache()
+        folded = residual_folded_block(cfg["tokens"], cfg["hidden"], cfg["inter"], sub_steps, args.warmup, flush, device)
+        torch.cuda.empty_cache()
         anchor = tp1_same_config(max(5, args.steps // 3), args.warmup, flush, device)
 
         gate_flops = 2.0 * cfg["tokens"] * cfg["hidden"] * 2 * cfg["inter"]
@@ -608,7 +609,8 @@ def run_ours(args, rank, world, device):
             "speedup_vs_dense_tcgen05_pct": by_tokens[str(cfg["tokens"])]["speedup_vs_dense_tcgen05_pct"],
             "speedup_vs_cublas_pct": by_tokens[str(cfg["tokens"])]["speedup_vs_cublas_pct"],
             "by_tokens": by_tokens, "roofline": roofline,
-            "sustained": sustained, "gemm_only": gemm_only, "tp1_same_config": anchor,
+            "sustained": sustained, "gemm_only": gemm_only, "residual_folded": folded,
+            "tp1_same_config": anchor,
             "cpu_baseline": cpu_baseline(cfg["hidden"], cfg["inter"]),
         }
         print(json.dumps(line))
@@ -798,6 +800,42 @@ def gemm_only_block(tokens, hidden, inter, steps, warmup, flush, device):
             "gate_up_speedup_pct": (t["gate_up_dense_tcgen05"] / t["gate_up_rank7"] - 1) * 100,
             "down_planes_speedup_pct": (t["down_dense_tcgen05"] / t["down_rank7_planes"] - 1) * 100,
             "down_ahead_speedup_pct": (t["down_dense_tcgen05"] / t["down_rank7_ahead"] - 1) * 100}
+
+
+def residual_folded_block(tokens, hidden, inter, steps, warmup, flush, device):
+    """The layer with its closing `x + mlp` folded into `down` (`Rank7MlpLayer(fuse_residual=True)`:
+    the gate_up kernel fills down's output with x instead of zeros and down reduce-adds onto it)
+    against the default layer, one graph replay per step, interleaved, cold L2; and what it costs:
+    both outputs against x + a dense cuBLAS evaluation of the MLP on 256 sampled rows."""
+    from lcgemm.layer import CapturedLayer, Rank7MlpLayer
+
+    x, nw, wgu, wd = make_layer_tensors(tokens, hidden, inter, device)
+    plain = Rank7MlpLayer(tokens, nw, wgu, wd, EPS)
+    try:
+        folded = Rank7MlpLayer(tokens, nw, wgu, wd, EPS, fuse_residual=True)
+    except ValueError as e:
+        return {"tokens": tokens, "unavailable": str(e)}
+    rows = torch.arange(0, tokens, max(1, tokens // 256), device=device)[:256]
+    xs = x[rows].float()
+    xn = (xs * torch.rsqrt(xs.square().mean(-1, keepdim=True) + EPS) * (nw.float() + 1)).to(torch.bfloat16)
+    zz = (xn @ wgu.t()).float()
+    sw = (torch.nn.functional.silu(zz[:, :inter]) * zz[:, inter:]).to(torch.bfloat16)
+    want = xs + (sw @ wd.t()).float()
+    rel = lambda o: ((o[rows].float() - want).norm() / want.norm()).item()
+    branch = lambda o: ((o[rows].float() - xs - (want - xs)).norm() / (want - xs).norm()).item()
+    err = {"plain_out_rel": rel(plain(x)), "folded_out_rel": rel(folded(x)),
+           "plain_branch_rel": branch(plain(x)), "folded_branch_rel": branch(folded(x))}
+    arms = {"plain": CapturedLayer(plain, x), "folded": CapturedLayer(folded, x)}
+    times = {k: [] for k in arms}
+    for _ in range(steps):
+        for name, fn in arms.items():
+            times[name] += _event_times(fn, 1, 0, flush)
+    from lcgemm import ops
+
+    ops.check_status()
+    t = {k: statistics.median(v) for k, v in times.items()}
+    return {"tokens": tokens, "ms": t, "saves_pct": (t["plain"] / t["folded"] - 1) * 100, **err,
+            "note": "off by default: every contribution of down is rounded at the magnitude of x"}
 
 
 def tp1_same_config(steps, warmup, flush, device):

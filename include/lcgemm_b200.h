@@ -229,6 +229,21 @@ int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_sche
                       void* preclear, int64_t preclear_bytes, int schedule, int cta_group,
                       int32_t* status, void* stream);
 
+/* The same kernel with the residual add of `down` folded into the chain.  No counterpart in the
+ * reference, whose `down` kernels have no residual operand: it leaves the add to the next layer's
+ * fused norm kernel (lcgemm/integrate/qwen_patch.py:160-167).  Instead of zeroing the rank-split consumer's output,
+ * the plane warps copy `init_from` (consumer_bytes, same layout as consumer_out, not overlapping
+ * it) into it, so every contribution the consumer reduce-adds lands on the residual stream and
+ * `consumer_out` ends as residual + down(...) without a separate add kernel.  Each contribution is
+ * then rounded to bf16 at the residual's magnitude instead of the branch's: see the numerics notes
+ * of the package before switching it on. */
+int lcg_gate_up_chain_init(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_scheme,
+                           const void* a_planes, int64_t ld_a, const void* b_planes, int64_t ld_b,
+                           void* z, int64_t ldz, int64_t M, int64_t N, int64_t K,
+                           void* down_planes, int64_t ld_planes,
+                           void* consumer_out, int64_t consumer_bytes, const void* init_from,
+                           int schedule, int cta_group, int32_t* status, void* stream);
+
 /* ---- tensor parallel over peer memory (NVLink / NVSwitch) ------------------
  * The reference runs on one GPU (lcgemm/integrate/qwen_patch.py:216-217 refuses TP > 1);
  * the three entry points below have no counterpart there.  One process per GPU; the caller

@@ -80,6 +80,15 @@ def test_describe_and_argument_checks_do_not_need_a_gpu(native_lib):
                                         80, None, 0, 0, 0, None, None) == nat.ERR_UNSUPPORTED_SHAPE
     assert native_lib.lcg_norm_planes(sch, fake, fake, fake, 7, 64, 1e-6, fake, fake, 64,
                                       None) == nat.ERR_UNSUPPORTED_SHAPE
+    # the chain with an initial content for the consumer output: it must exist, have somewhere to
+    # go and not be that output
+    other = ctypes.c_void_p(4096 + 160)
+    far = ctypes.c_void_p(1 << 20)
+    for consumer, nbytes, init in ((fake, 1600, None), (None, 0, far), (fake, 1600, other),
+                                   (fake, 1600, ctypes.c_void_p((1 << 20) + 8))):
+        assert native_lib.lcg_gate_up_chain_init(sch, sch, fake, 64, fake, 64, fake, 512, 64, 512, 128, fake,
+                                                 128, consumer, nbytes, init, 0, 0, None, None) in (
+            nat.ERR_BAD_ARG, nat.ERR_MISALIGNED)
     # a delta needs somewhere to store the sum; without a delta neither is needed (the shape check
     # comes next, so a missing delta is past the NULL check)
     assert native_lib.lcg_norm_planes(sch, fake, fake, fake, 8, 64, 1e-6, None, fake, 64,

@@ -145,6 +145,66 @@ def test_layer_without_a_delta_is_the_layer_with_a_zero_delta(lc):
     lc.ops.check_status()
 
 
+@pytest.mark.parametrize("dims", [(256, 256, 512), (512, 384, 1280), (130, 128, 256)])
+def test_residual_folded_into_down(lc, dims):
+    """The gate_up kernel fills the rank-split consumer's output with the residual stream instead
+    of zeros (bit for bit, checked before `down` runs); `down` then reduce-adds onto it and the
+    layer needs no add kernel.  Tolerances: against the unfused layer 6e-3 of the output (each of
+    down's contributions is rounded at the magnitude of h, ~2^-9 each), against the fp32 reference
+    the layer's usual 1.5e-2."""
+    m, h, i = dims
+    delta, x, nw, wgu, wd = _layer_inputs(m, h, i, seed=30)
+    gate, down = lc.seams.build_chain((m, h, 2 * i), (m, i, h))
+    assert down.rank_split and gate.preclear is down.c
+    gate.init_from = x
+    gate(x, None, nw, 1e-6, prepared_w=gate.prepare_weight(wgu))
+    assert torch.equal(down.c.view(torch.int16), x.view(torch.int16))
+    gate.init_from = None
+
+    plain = lc.layer.Rank7MlpLayer(m, nw, wgu, wd)
+    fused = lc.layer.Rank7MlpLayer(m, nw, wgu, wd, fuse_residual=True)
+    assert fused.fuse_residual and not plain.fuse_residual
+    for dl in (None, delta):
+        want = plain(x, dl).clone()
+        before = lc.ops.launch_count()
+        got = fused(x, dl)
+        mid = lc.ops.launch_count()
+        plain(x, dl)
+        assert mid - before == lc.ops.launch_count() - mid - 1          # one kernel less: no add
+        hh = x.cpu() if dl is None else (x.cpu().float() + dl.cpu().float()).to(torch.bfloat16)
+        ref, _ = O.mlp_reference(torch.zeros_like(hh) if dl is None else dl.cpu(), x.cpu(), nw.cpu(),
+                                 wgu.cpu(), wd.cpu(), 1e-6)
+        full = (hh.float() + ref.float()).to(torch.bfloat16)
+        assert rel_fro(got, want) <= 6e-3
+        assert rel_fro(got, full) <= 1.5e-2
+        # on the branch alone the roundings at |h| show (the branch is ~2 % of h at this size, so one
+        # rounding of the output is already ~10 % of it): a few such roundings instead of one
+        on_branch = lambda o: rel_fro(o.cpu().float() - hh.float(), ref.float())
+        assert on_branch(got) <= 3.0 * on_branch(want)
+        assert fused.gate_plan.init_from is None
+
+
+def test_residual_fold_refusals(lc, monkeypatch):
+    from lcgemm.seams import down as down_mod
+
+    m, h, i = 256, 256, 512
+    _, x, nw, wgu, wd = _layer_inputs(m, h, i, seed=31)
+    gate, down = lc.seams.build_chain((m, h, 2 * i), (m, i, h))
+    bw = gate.prepare_weight(wgu)
+    a = gate.a_planes(x, None, nw, 1e-6)
+    with pytest.raises(ValueError):                  # wrong shape
+        lc.ops.gate_up_chain(gate.scheme, gate.plane_scheme, a, bw, gate.c, gate.planes, preclear=down.c,
+                             init_from=x[:128])
+    with pytest.raises(ValueError):                  # nothing to write it to
+        lc.ops.gate_up_chain(gate.scheme, gate.plane_scheme, a, bw, gate.c, gate.planes, init_from=x)
+    with pytest.raises(Exception, match="overlaps"):  # the consumer output itself
+        lc.ops.gate_up_chain(gate.scheme, gate.plane_scheme, a, bw, gate.c, gate.planes, preclear=down.c,
+                             init_from=down.c)
+    monkeypatch.setattr(down_mod, "HYBRID_SHAPES", {(m, i, h)})
+    with pytest.raises(ValueError, match="rank-split"):
+        lc.layer.Rank7MlpLayer(m, nw, wgu, wd, fuse_residual=True)
+
+
 def test_plan_shape_errors(lc):
     gs, ds = lc.load(GATE), lc.load(DOWN)
     with pytest.raises(ValueError):

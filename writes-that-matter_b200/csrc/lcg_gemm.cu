@@ -103,8 +103,9 @@ struct ChainParams {
   int32_t plane_rank;
   int32_t iters_max;          // most work units any CTA group walks
   TermTable plane_terms;
-  uint4* preclear;            // consumer output to zero, or null
+  uint4* preclear;            // consumer output to zero (or to fill from `preload`), or null
   int64_t preclear_vecs;
+  const uint4* preload;       // what the consumer output starts from instead of zero, or null
 };
 
 // Tensor-parallel push: where the rows of this rank's finished C tiles go.  Row g of the (M, N)
@@ -899,9 +900,16 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
     auto clear_share = [&](int t) {
       if (ch.preclear == nullptr) return;
       const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-      for (int64_t i = (static_cast<int64_t>(t) * gridDim.x + blockIdx.x) * kPlaneThreads + ptid;
-           i < ch.preclear_vecs; i += clear_stride)
-        ch.preclear[i] = zero;
+      if (ch.preload == nullptr) {
+        for (int64_t i = (static_cast<int64_t>(t) * gridDim.x + blockIdx.x) * kPlaneThreads + ptid;
+             i < ch.preclear_vecs; i += clear_stride)
+          ch.preclear[i] = zero;
+      } else {
+        // The consumer adds its contributions onto the residual stream: start from that.
+        for (int64_t i = (static_cast<int64_t>(t) * gridDim.x + blockIdx.x) * kPlaneThreads + ptid;
+             i < ch.preclear_vecs; i += clear_stride)
+          ch.preclear[i] = __ldcs(ch.preload + i);
+      }
     };
     uint32_t seq = 0;
     for (int u = group_id; u < p.num_units; u += num_groups, ++seq) {
@@ -1495,14 +1503,23 @@ extern "C" int lcg_gemm_r7_slab(const lcg_scheme_t* scheme, const void* a_planes
   return cta_group == 1 ? launch<1, kModePlain>(ma, mb, mc, p, st_) : launch<2, kModePlain>(ma, mb, mc, p, st_);
 }
 
-extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_scheme,
-                                 const void* a_planes, int64_t ld_a, const void* b_planes,
-                                 int64_t ld_b, void* z, int64_t ldz, int64_t M, int64_t N, int64_t K,
-                                 void* down_planes, int64_t ld_planes, void* preclear,
-                                 int64_t preclear_bytes, int schedule, int cta_group,
-                                 int32_t* status, void* stream) {
+static int gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_scheme,
+                         const void* a_planes, int64_t ld_a, const void* b_planes, int64_t ld_b,
+                         void* z, int64_t ldz, int64_t M, int64_t N, int64_t K, void* down_planes,
+                         int64_t ld_planes, void* preclear, int64_t preclear_bytes,
+                         const void* preload, int schedule, int cta_group, int32_t* status,
+                         void* stream) {
   if (!scheme || !plane_scheme || !a_planes || !b_planes || !z || !down_planes)
     return fail(LCG_ERR_BAD_ARG, "NULL operand");
+  if (preload != nullptr) {
+    if (preclear == nullptr || preclear_bytes <= 0)
+      return fail(LCG_ERR_BAD_ARG, "an initial content needs the consumer output it is written to");
+    if ((reinterpret_cast<uintptr_t>(preload) & 15u) != 0)
+      return fail(LCG_ERR_MISALIGNED, "the initial content must be 16-byte aligned");
+    const auto a0 = reinterpret_cast<uintptr_t>(preload), b0 = reinterpret_cast<uintptr_t>(preclear);
+    if (a0 < b0 + static_cast<uintptr_t>(preclear_bytes) && b0 < a0 + static_cast<uintptr_t>(preclear_bytes))
+      return fail(LCG_ERR_BAD_ARG, "the initial content overlaps the consumer output");
+  }
   if (schedule != LCG_SCHEDULE_ALL_RANKS && schedule != LCG_SCHEDULE_HYBRID)
     return fail(LCG_ERR_BAD_ARG, "the chained GEMM runs the all-ranks or the hybrid schedule, got %d",
                 schedule);
@@ -1544,6 +1561,7 @@ extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t*
     for (int x = 0; x < 4; ++x) ch.plane_terms.coef[r][x] = static_cast<float>(plane_scheme->a[r][x]);
   ch.preclear = preclear_bytes > 0 ? static_cast<uint4*>(preclear) : nullptr;
   ch.preclear_vecs = preclear_bytes / 16;
+  ch.preload = ch.preclear != nullptr ? static_cast<const uint4*>(preload) : nullptr;
   auto st_ = static_cast<cudaStream_t>(stream);
   if (int e = zero_tail_tiles(p, z, ldz, M, N, g, cta_group, st_)) return e;
   // The plane phase is compiled for the shipped `down` scheme's A table; any other table runs
@@ -1566,6 +1584,28 @@ extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t*
     count_launch();
   }
   return LCG_OK;
+}
+
+extern "C" int lcg_gate_up_chain(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_scheme,
+                                 const void* a_planes, int64_t ld_a, const void* b_planes,
+                                 int64_t ld_b, void* z, int64_t ldz, int64_t M, int64_t N, int64_t K,
+                                 void* down_planes, int64_t ld_planes, void* preclear,
+                                 int64_t preclear_bytes, int schedule, int cta_group,
+                                 int32_t* status, void* stream) {
+  return gate_up_chain(scheme, plane_scheme, a_planes, ld_a, b_planes, ld_b, z, ldz, M, N, K, down_planes,
+                       ld_planes, preclear, preclear_bytes, nullptr, schedule, cta_group, status, stream);
+}
+
+extern "C" int lcg_gate_up_chain_init(const lcg_scheme_t* scheme, const lcg_scheme_t* plane_scheme,
+                                      const void* a_planes, int64_t ld_a, const void* b_planes,
+                                      int64_t ld_b, void* z, int64_t ldz, int64_t M, int64_t N,
+                                      int64_t K, void* down_planes, int64_t ld_planes, void* consumer_out,
+                                      int64_t consumer_bytes, const void* init_from, int schedule,
+                                      int cta_group, int32_t* status, void* stream) {
+  if (!init_from) return fail(LCG_ERR_BAD_ARG, "NULL initial content");
+  return gate_up_chain(scheme, plane_scheme, a_planes, ld_a, b_planes, ld_b, z, ldz, M, N, K, down_planes,
+                       ld_planes, consumer_out, consumer_bytes, init_from, schedule, cta_group, status,
+                       stream);
 }
 
 extern "C" int lcg_gemm_r7_push(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,

@@ -53,6 +53,8 @@ SIGNATURES = {
                                 _i32, _i32, _i32, _vp, _vp]),
     "lcg_gate_up_chain": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
                                  _vp, _i64, _vp, _i64, _i32, _i32, _vp, _vp]),
+    "lcg_gate_up_chain_init": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
+                                      _vp, _i64, _vp, _i64, _vp, _i32, _i32, _vp, _vp]),
     "lcg_gemm_r7_push": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _i32,
                                 _i64, _i32, _vp, _vp]),
     "lcg_peer_barrier": (_i32, [_vp, _i32, _i32, _c.c_uint32, _i64, _vp, _vp]),

@@ -21,7 +21,7 @@ from .seams import build_chain
 
 class Rank7MlpLayer:
     def __init__(self, tokens: int, norm_weight, gate_up_weight, down_weight, eps: float = 1e-6,
-                 cta_group: int = 0):
+                 cta_group: int = 0, fuse_residual: bool = False):
         two_i, hidden = gate_up_weight.shape
         out_dim, inter = down_weight.shape
         if two_i != 2 * inter:
@@ -33,6 +33,16 @@ class Rank7MlpLayer:
         self.gate_bw = self.gate_plan.prepare_weight(gate_up_weight)
         self.down_bw = self.down_plan.prepare_weight(down_weight)
         self.out = torch.empty((tokens, out_dim), device=gate_up_weight.device, dtype=torch.bfloat16)
+        # fuse_residual: the closing `h + mlp` is folded into `down`.  Possible when `down` is
+        # rank-split and its output is initialised by the gate_up kernel: that kernel then copies h
+        # into it instead of zeroing it, every contribution of `down` is reduce-added onto h, and no
+        # add kernel runs.  Off by default: each contribution is then rounded to bf16 at the
+        # magnitude of h instead of the branch's (about three times the error on the output).
+        self.fuse_residual = bool(fuse_residual) and self.down_plan.rank_split \
+            and self.gate_plan.preclear is self.down_plan.c and out_dim == hidden \
+            and self.down_plan.c.is_contiguous()
+        if fuse_residual and not self.fuse_residual:
+            raise ValueError("fuse_residual needs a rank-split `down` whose output the gate_up kernel initialises")
 
     def chain(self, delta, residual):
         """``(down_out, residual_out)`` exactly as the custom op returns them.  Without a ``delta``
@@ -44,6 +54,15 @@ class Rank7MlpLayer:
 
     def forward(self, x, delta=None):
         """``h + mlp(norm(h))`` with ``h = x + delta`` (``h = x`` without a ``delta``)."""
+        if self.fuse_residual:
+            gate = self.gate_plan
+            # h is x without a delta, else what the norm kernel stores in front of the GEMM
+            gate.init_from = x if delta is None else gate.residual_out
+            try:
+                down_out, _ = self.chain(delta, x)
+            finally:
+                gate.init_from = None
+            return down_out
         down_out, h = self.chain(delta, x)
         return ops.add(h, down_out if down_out.is_contiguous() else down_out.contiguous(), out=self.out)
 

@@ -332,7 +332,10 @@ def bare_gemm_form(m: int, n: int, k: int):
 
 
 def gate_up_chain(scheme, plane_scheme, a_pl, b_pl, z, down_planes, preclear=None,
-                  schedule: int = nat.SCHEDULE_HYBRID, cta_group: int = 0) -> None:
+                  schedule: int = nat.SCHEDULE_HYBRID, cta_group: int = 0, init_from=None) -> None:
+    """The chained gate_up GEMM.  ``preclear``: the rank-split consumer's output, zeroed while the
+    kernel runs -- or, with ``init_from`` (same shape, contiguous, another buffer), filled with it, so
+    that the consumer's reduce-adds land on the residual stream."""
     for t, what in ((a_pl, "A planes"), (b_pl, "B planes"), (z, "z"), (down_planes, "down planes")):
         _need(t, what)
     m, n = z.shape
@@ -348,6 +351,15 @@ def gate_up_chain(scheme, plane_scheme, a_pl, b_pl, z, down_planes, preclear=Non
         if not preclear.is_contiguous():
             raise ValueError("the consumer output to clear must be contiguous")
         pc_ptr, pc_bytes = ptr(preclear), preclear.numel() * preclear.element_size()
+    if init_from is not None:
+        _need(init_from, "initial content")
+        if preclear is None or tuple(init_from.shape) != tuple(preclear.shape) or not init_from.is_contiguous():
+            raise ValueError("the initial content must be a contiguous tensor of the consumer output's shape")
+        check(lib().lcg_gate_up_chain_init(
+            NativeScheme.of(scheme).handle, NativeScheme.of(plane_scheme).handle, ptr(a_pl), a_pl.stride(0),
+            ptr(b_pl), b_pl.stride(0), ptr(z), z.stride(0), m, n, k, ptr(down_planes), down_planes.stride(0),
+            pc_ptr, pc_bytes, ptr(init_from), schedule, cta_group, ptr(status_word(z.device)), stream_ptr()))
+        return
     check(lib().lcg_gate_up_chain(NativeScheme.of(scheme).handle, NativeScheme.of(plane_scheme).handle,
                                   ptr(a_pl), a_pl.stride(0), ptr(b_pl), b_pl.stride(0), ptr(z),
                                   z.stride(0), m, n, k, ptr(down_planes), down_planes.stride(0),

@@ -46,6 +46,9 @@ class GateUpPlan:
         self.planes = torch.empty((plane_scheme.rank * (m // 2), (n // 2) // 2), device=dev, dtype=bf)
         # The consumer's output when it must arrive zeroed; ``self.c`` means "nothing to clear".
         self.preclear = self.c
+        # What that output starts from instead of zero (the residual stream, when the layer folds
+        # its closing add into the consumer's reduce-adds); None: zero.
+        self.init_from = None
         self._desc = None
 
     # ---------------------------------------------------------------- offline
@@ -63,7 +66,8 @@ class GateUpPlan:
         c = self.c if out is None else out
         ops.gate_up_chain(self.scheme, self.plane_scheme, a_planes, prepared_w, c, self.planes,
                           preclear=None if self.preclear is self.c else self.preclear,
-                          schedule=self.schedule, cta_group=self.cta_group)
+                          schedule=self.schedule, cta_group=self.cta_group,
+                          init_from=None if self.preclear is self.c else self.init_from)
         return c
 
     def __call__(self, *pre_inputs, prepared_w, out=None, residual_out=None):
