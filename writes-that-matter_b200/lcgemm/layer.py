@@ -37,7 +37,7 @@ class Rank7MlpLayer:
         # rank-split and its output is initialised by the gate_up kernel: that kernel then copies h
         # into it instead of zeroing it, every contribution of `down` is reduce-added onto h, and no
         # add kernel runs.  Off by default: each contribution is then rounded to bf16 at the
-        # magnitude of h instead of the branch's (about three times the error on the output).
+        # magnitude of h instead of the branch's (1.7 times the error on the MLP branch where h dominates it).
         self.fuse_residual = bool(fuse_residual) and self.down_plan.rank_split \
             and self.gate_plan.preclear is self.down_plan.c and out_dim == hidden \
             and self.down_plan.c.is_contiguous()
