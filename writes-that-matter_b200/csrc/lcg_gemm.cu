@@ -164,6 +164,7 @@ struct GemmParams {
   int32_t zero_tail;
   int32_t tiles_m, tiles_n, group_m;
   int32_t tm_base;            // first tile row of this launch (a slab of tile rows; 0 = from the top)
+  int32_t tm_rot;             // the walk starts this many tile rows down and wraps (tensor-parallel push)
   int32_t max_groups;         // cap on CTA groups (0 = all SMs); leaves SMs to a concurrent kernel
   int32_t num_units;
   int32_t k_blocks;
@@ -191,7 +192,8 @@ __device__ __forceinline__ void tile_coord(const GemmParams& p, int t, int& tm, 
   const int band = t / band_sz;
   const int rem = t - band * band_sz;
   const int gm = min(p.group_m, p.tiles_m - band * p.group_m);
-  tm = p.tm_base + band * p.group_m + rem % gm;
+  tm = band * p.group_m + rem % gm + p.tm_rot;
+  tm = p.tm_base + (tm >= p.tiles_m ? tm - p.tiles_m : tm);
   tn = rem / gm;
 }
 __device__ __forceinline__ UnitCoord decode_unit(const GemmParams& p, int u) {
@@ -1649,6 +1651,10 @@ extern "C" int lcg_gemm_r7_push(const lcg_scheme_t* scheme, const void* a_planes
   pp.n = static_cast<int32_t>(N);
   pp.m2 = static_cast<int32_t>(g.m2);
   pp.n2 = static_cast<int32_t>(g.n2);
+  // Every rank walks the tile rows in the same order, and a tile row's rows belong to two owners: left
+  // alone, all ranks push to the same two owners at any moment and those two inbound links carry the
+  // whole exchange while the others idle.  Rank r therefore starts its walk r / world of the way down.
+  p.tm_rot = static_cast<int32_t>((static_cast<int64_t>(rank) * p.tiles_m) / world);
   auto st_ = static_cast<cudaStream_t>(stream);
   if (int e = zero_tail_tiles(p, c, ldc, M, N, g, cta_group, st_)) return e;
   if (int e = cta_group == 1 ? launch<1, kModePush>(ma, mb, mc, p, st_) : launch<2, kModePush>(ma, mb, mc, p, st_))
