@@ -1003,6 +1003,17 @@ def run_case(args, device):
         scr = torch.empty(ops.ahead_scratch_bytes(lead, m, i), dtype=torch.uint8, device=device)
         out = torch.empty((m, h), device=device, dtype=torch.bfloat16)
         fn, flops = (lambda: ops.gemm_r7_ahead(s_tok, bp, h, lead, out=out, scratch=scr)), 2.0 * m * i * h
+    elif args.case == "down_push_local":
+        # one rank's row-parallel `down` of the tensor-parallel layer (K = --inter is the rank's shard)
+        # with the push to the owners' slots, every slot in this GPU's memory: the kernel without the link
+        world = 8
+        loc = S.load("2x2_locality_ordered")
+        s_tok = torch.randn((m, i), device=device).to(torch.bfloat16)
+        ap, bp = ops.a_planes(s_tok, loc), ops.prepare_b(wd, loc)
+        out = torch.empty((m, h), device=device, dtype=torch.bfloat16)
+        slots = [torch.empty((m // world, h), device=device, dtype=torch.bfloat16) for _ in range(world)]
+        ptrs = [t.data_ptr() for t in slots]
+        fn, flops = (lambda: ops.gemm_r7_push(loc, ap, bp, m, h, i, out, ptrs, 3, m // world)), 2.0 * m * i * h
     elif args.case == "dense_gate_up":
         out = torch.empty((m, 2 * i), device=device, dtype=torch.bfloat16)
         fn, flops = (lambda: ops.gemm_dense(x, wgu, out=out)), 2.0 * m * h * 2 * i
@@ -1354,7 +1365,7 @@ def main():
     ap.add_argument("--prompts", type=int, default=8, help="seeded prompts per length for --model's agreement rates")
     ap.add_argument("--model-tokens", default="2048,4096,8192", help="prompt lengths for --model")
     ap.add_argument("--case", default=None,
-                    help="time one kernel alone: gate_up | down | norm_planes | norm_planes_single | a_planes | bare_ahead | dense_gate_up; "
+                    help="time one kernel alone: gate_up | down | norm_planes | norm_planes_single | a_planes | bare_ahead | down_push_local | dense_gate_up; "
                          "or `layer`: the whole layer's three arms at --tokens / --hidden / --inter")
     ap.add_argument("--tokens", type=int, default=4096, help="token count for --case")
     ap.add_argument("--hidden", type=int, default=SINGLE["hidden"], help="hidden size for --case")
