@@ -634,11 +634,6 @@ def run_ours(args, rank, world, device):
             if rank == 0:
                 print(json.dumps({"error": "tensor-parallel output failed its parity check", "parity": parity}))
             raise SystemExit(3)
-    anchor = None
-    if args.tp1_anchor:
-        if rank == 0:
-            anchor = tp1_same_config(max(5, args.steps // 3), args.warmup, flush, device)
-        dist.barrier()
     launches0 = ops.launch_count()
     layer(x)
     launches = (ops.launch_count() - launches0) * args.steps
@@ -672,6 +667,13 @@ def run_ours(args, rank, world, device):
     e2e_stream_ms = streamed_e2e_ms(layer, cfg["tokens"], cfg["hidden"], x_slice, out_slice, args,
                                     sync_all, group=dist.group.WORLD, timeline=timeline)
     phases = tp_phase_times(layer, x, args.steps, flush, sync_all) if args.exchange == "peer" else None
+    # The one-GPU anchor comes last: run in front of the timed steps it leaves rank 0's GPU hot and
+    # power-limited while the others are cool, and every step then waits for rank 0.
+    anchor = None
+    if args.tp1_anchor:
+        if rank == 0:
+            anchor = tp1_same_config(max(5, args.steps // 3), args.warmup, flush, device)
+        dist.barrier()
     t = torch.tensor([statistics.mean(times), e2e_stream_ms, statistics.mean(e2e_times)], device=device,
                      dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)

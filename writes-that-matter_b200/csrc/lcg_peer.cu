@@ -83,7 +83,7 @@ __device__ __forceinline__ void add8(const uint4& q, float (&acc)[8]) {
 
 // out[rank's rows] = bf16(h + sum_w slots[w]) in fp32, ranks summed in index order, stored into
 // all ranks' outputs (the all-gather half).  One 16-byte vector per thread and iteration.
-__global__ void __launch_bounds__(256) k_reduce_gather(const GatherArgs a) {
+__global__ void __launch_bounds__(256) k_reduce_gather(const __grid_constant__ GatherArgs a) {
   const int64_t vec_per_row = a.cols / 8;
   const int64_t row0 = static_cast<int64_t>(a.rank) * a.rows_per_owner;
   const int64_t rows = min(a.rows_per_owner, a.m - row0);
@@ -114,10 +114,16 @@ __global__ void __launch_bounds__(256) k_reduce_gather(const GatherArgs a) {
     o.y = *reinterpret_cast<const uint32_t*>(&p1);
     o.z = *reinterpret_cast<const uint32_t*>(&p2);
     o.w = *reinterpret_cast<const uint32_t*>(&p3);
+    // Peers in the order rank + 1, rank + 2, ..., own copy last: the ranks run this kernel at the
+    // same time, and all of them storing to peer 0 first, then peer 1, would crowd one link at a time.
     const int64_t off = (row0 + lr) * a.cols + c;
 #pragma unroll
-    for (int w = 0; w < kMaxWorld; ++w)
-      if (w < a.world) __stcg(reinterpret_cast<uint4*>(a.out[w] + off), o);
+    for (int j = 1; j <= kMaxWorld; ++j)
+      if (j <= a.world) {
+        int w = a.rank + j;
+        if (w >= a.world) w -= a.world;
+        __stcg(reinterpret_cast<uint4*>(a.out[w] + off), o);
+      }
   }
 }
 

@@ -106,7 +106,11 @@ class HostStreamedLayer:
             if self.gather == "copy":
                 # Safe to overwrite the peers' buffer i: a rank frees it only after its layer call,
                 # whose closing barrier every rank passes after all of them have read their input.
-                for p in range(self.world):
+                # Rank r copies to r + 1, r + 2, ... and to itself last: at any moment every rank's
+                # inbound link carries one copy (all ranks copying to peer 0 first, then to peer 1, would
+                # queue the whole replication behind one link at a time).
+                for j in range(1, self.world + 1):
+                    p = (self.rank + j) % self.world
                     self.peer_rows[i][p].copy_(self.x_in[i], non_blocking=True)
             if ev:
                 ev["in1"].record()
