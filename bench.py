@@ -672,7 +672,10 @@ def run_ours(args, rank, world, device):
     anchor = None
     if args.tp1_anchor:
         if rank == 0:
+            torch.cuda.synchronize()
+            time.sleep(2.0)      # let the GPU leave the power-limited state the runs above put it in
             anchor = tp1_same_config(max(5, args.steps // 3), args.warmup, flush, device)
+            anchor["when"] = "after the timed steps and a 2 s pause, on rank 0 alone"
         dist.barrier()
     t = torch.tensor([statistics.mean(times), e2e_stream_ms, statistics.mean(e2e_times)], device=device,
                      dtype=torch.float64)
