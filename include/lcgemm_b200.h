@@ -255,7 +255,9 @@ int lcg_gate_up_chain_init(const lcg_scheme_t* scheme, const lcg_scheme_t* plane
  * owns its rows: row g belongs to rank g / rows_per_owner and lands in slots[owner], an
  * (rows_per_owner, N) row-major region of the owner's memory reserved for this rank
  * (slots is a host array of `world` device pointers; slots[rank] is local).  The tail tiles
- * of the hybrid schedule are pushed by a small second kernel behind the GEMM.  N % 8 == 0,
+ * of the hybrid schedule are pushed by a small second kernel behind the GEMM.  Rank r starts its
+ * walk over the tile rows r / world of the way down (and wraps), so that the ranks, which run this
+ * kernel together, push to different owners at any moment instead of all to the same two.  N % 8 == 0,
  * c 16-byte aligned, ldc % 8 == 0, world <= 8. */
 int lcg_gemm_r7_push(const lcg_scheme_t* scheme, const void* a_planes, int64_t ld_a,
                      const void* b_planes, int64_t ld_b, void* c, int64_t ldc,
