@@ -487,8 +487,12 @@ def bench_layer_arms(tokens, hidden, inter, steps, warmup, flush, device, with_p
         collecting[0] = True
     launches0 = ops.launch_count()
     times = {k: [] for k in arms}
-    for _ in range(steps):
-        for name, fn in arms.items():
+    names = list(arms)
+    for s in range(steps):
+        # the arm that goes first rotates: an arm that always ran behind the other two would always
+        # start from the hottest, most power-limited GPU
+        for name in names[s % len(names):] + names[:s % len(names)]:
+            fn = arms[name]
             flush.zero_()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -608,6 +612,9 @@ def run_ours(args, rank, world, device):
             "gpu_launches": head["launches"],
             "speedup_vs_dense_tcgen05_pct": by_tokens[str(cfg["tokens"])]["speedup_vs_dense_tcgen05_pct"],
             "speedup_vs_cublas_pct": by_tokens[str(cfg["tokens"])]["speedup_vs_cublas_pct"],
+            "speedup_note": "arms alternate step by step on one GPU under one power limiter, which flatters "
+                            "the hungrier rank-7 arm; `sustained` (blocks per arm) and `bench.py --rounds R` "
+                            "(a fresh process per arm) are the fair comparisons",
             "by_tokens": by_tokens, "roofline": roofline,
             "sustained": sustained, "gemm_only": gemm_only, "residual_folded": folded,
             "tp1_same_config": anchor,
