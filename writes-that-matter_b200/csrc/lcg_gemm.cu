@@ -600,7 +600,10 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
         tcgen05_fence_after();
         const StepDesc& sd = uc.split ? p.steps_split[s] : p.steps[s];
         for (int g = 0; g < sd.ngroups; ++g) {
-          const float coeff = static_cast<float>(sd.group[g].coeff);
+          // +1 and -1 (every shipped table) need no multiplication: rounding to bf16 is symmetric, so
+          // -1 is a flip of the packed sign bits after the conversion.  Same bits, half the arithmetic.
+          const int coeff_i = sd.group[g].coeff;
+          const float coeff = static_cast<float>(coeff_i);
 #pragma unroll 1
           for (int sub = 0; sub < kBN / kEpiCols; ++sub, ++epi_it) {
             uint32_t r0[32], r1[32];
@@ -610,12 +613,24 @@ k_gemm(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtens
             tmem_ld_32x32(taddr + 32, r1);
             tmem_ld_wait();
             uint32_t pk[32];
+            if (coeff_i == 1 || coeff_i == -1) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              pk[j] = pack_bf16x2(coeff * __uint_as_float(r0[2 * j]),
-                                  coeff * __uint_as_float(r0[2 * j + 1]));
-              pk[16 + j] = pack_bf16x2(coeff * __uint_as_float(r1[2 * j]),
-                                       coeff * __uint_as_float(r1[2 * j + 1]));
+              for (int j = 0; j < 16; ++j) {
+                pk[j] = pack_bf16x2(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+                pk[16 + j] = pack_bf16x2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+              }
+              if (coeff_i < 0) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) pk[j] ^= 0x80008000u;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                pk[j] = pack_bf16x2(coeff * __uint_as_float(r0[2 * j]),
+                                    coeff * __uint_as_float(r0[2 * j + 1]));
+                pk[16 + j] = pack_bf16x2(coeff * __uint_as_float(r1[2 * j]),
+                                         coeff * __uint_as_float(r1[2 * j + 1]));
+              }
             }
             const uint32_t buf = epi_base + (epi_it & 1u) * kEpiBytes;
             // The bulk copy issued two sub-tiles ago read this buffer; it must be done.
