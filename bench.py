@@ -10,8 +10,10 @@ N = 1   one "step" = one fused MLP layer of the single-layer configuration
         (4096 tokens x hidden 5120, intermediate 17408): fused residual+RMSNorm+A planes,
         chained rank-7 gate_up GEMM (SwiGLU + down's A planes in its epilogue), rank-split
         rank-7 down GEMM, residual add.  The dense arms (own tcgen05 GEMM, cuBLAS) run
-        interleaved in the same process for the speedup figures, and 2048 / 8192 tokens are
-        measured beside the headline 4096.
+        interleaved in the same process for the speedup figures (which arm goes first rotates
+        step by step), and 2048 / 8192 tokens are measured beside the headline 4096.  Arms that
+        alternate on one GPU share its power limiter, which flatters the hungrier rank-7 arm:
+        `sustained` and --rounds are the fair comparisons (`speedup_note` says so in the line).
 N > 1   the tensor-parallel configuration (8192 tokens, hidden 8192, intermediate 28672)
         split over the intermediate dimension; the ranks' partial outputs are combined by
         the package's own kernels over NVLink peer memory (--exchange peer: pushed from inside
@@ -28,10 +30,12 @@ is reported beside it (`serial_ms_per_step`).
 
 The N = 1 line also carries `sustained` (both layer arms run back to back for seconds, in
 alternating blocks, with the SM clock sampled per arm), `gemm_only` (the two GEMMs without
-their seams, rank-7 against dense tcgen05) and `tp1_same_config` (the tensor-parallel
+their seams, rank-7 against dense tcgen05), `residual_folded` (the layer with its closing add
+folded into `down`, an option that is off by default) and `tp1_same_config` (the tensor-parallel
 configuration on one GPU: the anchor of the strong-scaling curve); the N > 1 line carries
 `parity` (the fused exchange's output against the NCCL exchange and against a dense cuBLAS
-evaluation of a row sample, checked before anything is timed) and the same anchor.
+evaluation of a row sample, checked before anything is timed), `phases_ms` and the same anchor,
+measured on rank 0 after the timed steps.
 
 --impl reference times the reference's own CPU evaluation of the scheme on the host cores
 (its torch functions from the unmodified install under baseline/_ref when that is present,
